@@ -1,0 +1,107 @@
+"""In-tree build of libdpnp_b200.so with nvcc for sm_100a.
+
+``python -m dpnp_b200._build`` compiles every source under ``csrc/`` into an
+object file (in parallel, skipping objects newer than all sources and headers)
+and links them into ``dpnp_b200/libdpnp_b200.so``.  The CUDA runtime is linked
+statically, so the library needs only the driver at run time.
+"""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ_DIR = os.path.join(HERE, "build")
+LIB_PATH = os.path.join(HERE, "libdpnp_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode",
+    "arch=compute_100a,code=sm_100a",
+    "-lineinfo",
+    "-O3",
+    "-std=c++17",
+    "-fmad=false",  # every multiply and add rounds on its own, as the per-op reference kernels do
+    "--expt-relaxed-constexpr",
+    "-Xcompiler",
+    "-fPIC",
+    "-diag-suppress=128",  # "loop is not reachable": if-constexpr branches that return early
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or add it to PATH")
+
+
+def _sources() -> list[str]:
+    return sorted(
+        os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp"))
+    )
+
+
+def _headers_mtime() -> float:
+    newest = 0.0
+    for root in (CSRC, os.path.join(HERE, os.pardir, "include")):
+        for f in os.listdir(root):
+            if f.endswith((".h", ".cuh", ".hpp")):
+                newest = max(newest, os.path.getmtime(os.path.join(root, f)))
+    return newest
+
+
+def _compile_one(nvcc: str, src: str, obj: str, extra: list[str]) -> tuple[str, int, str]:
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-x", "cu", "-c", src, "-o", obj]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    return src, proc.returncode, proc.stdout + proc.stderr
+
+
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None,
+          ptxas_info: bool = False) -> str:
+    """Compile and link the library; returns its path."""
+    nvcc = _nvcc()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    hdr_time = _headers_mtime()
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    todo = []
+    objs = []
+    for src in _sources():
+        obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
+        objs.append(obj)
+        if (
+            force
+            or ptxas_info
+            or not os.path.exists(obj)
+            or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time)
+        ):
+            todo.append((src, obj))
+    if todo:
+        jobs = jobs or max(1, (os.cpu_count() or 2))
+        with ThreadPoolExecutor(max_workers=jobs) as pool:
+            results = list(pool.map(lambda so: _compile_one(nvcc, so[0], so[1], extra), todo))
+        failed = False
+        for src, rc, out in results:
+            if verbose or rc != 0 or ptxas_info:
+                sys.stderr.write(f"[nvcc] {os.path.basename(src)} -> rc={rc}\n{out}\n")
+            failed = failed or rc != 0
+        if failed:
+            raise RuntimeError("compilation of libdpnp_b200 failed")
+    if todo or not os.path.exists(LIB_PATH):
+        link = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode",
+                "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
+        proc = subprocess.run(link, capture_output=True, text=True)
+        if proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+            raise RuntimeError("link of libdpnp_b200.so failed")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                 ptxas_info="--ptxas" in sys.argv)
+    print(path)

@@ -1,0 +1,516 @@
+// Elementwise engine: kernel templates and their typed launcher.
+//
+// A functor F describes one elementwise operation:
+//   F::NIN            number of inputs (0..3)
+//   F::In0/In1/In2    input element types (unused ones are char)
+//   F::Out            output element type
+//   Out operator()(In0[, In1[, In2]]) const
+// Four kernel families serve every F:
+//   ew_contig_vec / ew_contig_scalar  contiguous operands (any input may be a
+//                                     broadcast scalar), 16-byte accesses when
+//                                     every pointer allows it
+//   ew_rows        innermost dimension unit-stride (or broadcast) in every
+//                  operand, outer dimensions arbitrary
+//   ew_transpose   one or more inputs contiguous along a different dimension
+//                  than the output: 32x32 shared-memory tile
+//   ew_generic     anything else: one element per thread-iteration, collapsed
+//                  shape/strides in kernel parameters, multiply-shift division
+//
+// These replace the reference's Unary/Binary Contig and Strided functors and
+// launchers (dpnp/tensor/libtensor/include/kernels/elementwise_functions/common.hpp:64-273,
+// 302-389,398-558,779-884), the where kernels (include/kernels/where.hpp:67-313) and the
+// copy/cast kernels (include/kernels/copy_and_cast.hpp:90-389).
+#pragma once
+
+#include "common.cuh"
+#include "ew_plan.h"
+
+namespace dpb {
+
+constexpr int kEwThreads = 256;
+
+template <class F> struct EwPtrs {
+    const void *in[3];
+    void *out;
+};
+
+template <int NARR> struct StridedMeta {
+    int nd;
+    int64_t shape[kMaxD];
+    int64_t strides[NARR][kMaxD];
+    FastDiv32 div[kMaxD];
+};
+
+template <class F, class A, class B, class C>
+DPB_D typename F::Out ew_apply(const F &f, A a, B b, C c)
+{
+    if constexpr (F::NIN == 0) return f();
+    else if constexpr (F::NIN == 1) return f(a);
+    else if constexpr (F::NIN == 2) return f(a, b);
+    else return f(a, b, c);
+}
+
+template <class F> constexpr int ew_vec_width()
+{
+    if constexpr (F::NIN == 0) return vec_width<typename F::Out>();
+    else if constexpr (F::NIN == 1) return vec_width<typename F::In0, typename F::Out>();
+    else if constexpr (F::NIN == 2)
+        return vec_width<typename F::In0, typename F::In1, typename F::Out>();
+    else return vec_width<typename F::In0, typename F::In1, typename F::In2, typename F::Out>();
+}
+
+// ------------------------------------------------------------- contiguous
+// Tile = 256 threads x VEC elements x UNROLL vectors; blocks walk the tiles
+// with a grid stride; the ragged end is handled element-wise by one block.
+template <class F, int VEC, int UNROLL>
+__global__ void __launch_bounds__(kEwThreads)
+    ew_contig_vec_kernel(F f, EwPtrs<F> p, int64_t n, unsigned bcast)
+{
+    using In0 = typename F::In0;
+    using In1 = typename F::In1;
+    using In2 = typename F::In2;
+    using Out = typename F::Out;
+    constexpr int64_t TILE = int64_t(kEwThreads) * VEC * UNROLL;
+    const In0 *a = static_cast<const In0 *>(p.in[0]);
+    const In1 *b = static_cast<const In1 *>(p.in[1]);
+    const In2 *c = static_cast<const In2 *>(p.in[2]);
+    Out *o = static_cast<Out *>(p.out);
+
+    In0 sa{};
+    In1 sb{};
+    In2 sc{};
+    if constexpr (F::NIN >= 1) { if (bcast & 1u) sa = a[0]; }
+    if constexpr (F::NIN >= 2) { if (bcast & 2u) sb = b[0]; }
+    if constexpr (F::NIN >= 3) { if (bcast & 4u) sc = c[0]; }
+
+    const int64_t ntiles = n / TILE;
+    for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int64_t base = t * TILE + int64_t(threadIdx.x) * VEC;
+        vec_t<In0, VEC> va[UNROLL];
+        vec_t<In1, VEC> vb[UNROLL];
+        vec_t<In2, VEC> vc[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t i = base + int64_t(u) * kEwThreads * VEC;
+            if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) va[u] = load_vec<vec_t<In0, VEC>>(a + i); }
+            if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) vb[u] = load_vec<vec_t<In1, VEC>>(b + i); }
+            if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) vc[u] = load_vec<vec_t<In2, VEC>>(c + i); }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t i = base + int64_t(u) * kEwThreads * VEC;
+            vec_t<Out, VEC> r;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                In0 x = sa;
+                In1 y = sb;
+                In2 z = sc;
+                if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) x = va[u].v[k]; }
+                if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) y = vb[u].v[k]; }
+                if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) z = vc[u].v[k]; }
+                r.v[k] = ew_apply(f, x, y, z);
+            }
+            store_vec(o + i, r);
+        }
+    }
+    if (blockIdx.x == static_cast<unsigned>(ntiles % gridDim.x)) {
+        for (int64_t i = ntiles * TILE + threadIdx.x; i < n; i += kEwThreads) {
+            In0 x = sa;
+            In1 y = sb;
+            In2 z = sc;
+            if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) x = a[i]; }
+            if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) y = b[i]; }
+            if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) z = c[i]; }
+            o[i] = ew_apply(f, x, y, z);
+        }
+    }
+}
+
+// ------------------------------------------------------------------- rows
+// The innermost collapsed dimension (length L) has stride 0 or 1 in every
+// operand; `outer` describes the remaining dimensions.  A block is TX threads
+// along the row times TY rows; a work item is (row group, chunk of the row).
+template <class F, int VEC, int UNROLL>
+__global__ void __launch_bounds__(kEwThreads)
+    ew_rows_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> outer, int64_t L, unsigned inner_bcast,
+                   int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork)
+{
+    using In0 = typename F::In0;
+    using In1 = typename F::In1;
+    using In2 = typename F::In2;
+    using Out = typename F::Out;
+    constexpr int NARR = F::NIN + 1;
+    const int TX = 1 << tx_log2;
+    const int TY = kEwThreads >> tx_log2;
+    const int tx = threadIdx.x & (TX - 1);
+    const int ty = threadIdx.x >> tx_log2;
+
+    for (int64_t w = blockIdx.x; w < nwork; w += gridDim.x) {
+        const int64_t rg = w / chunks_per_row;
+        const int64_t chunk = w - rg * chunks_per_row;
+        const int64_t row = rg * TY + ty;
+        if (row >= nrows) continue;
+        // row -> offsets of the row start in every array
+        int64_t off[NARR];
+#pragma unroll
+        for (int k = 0; k < NARR; ++k) off[k] = 0;
+        {
+            uint32_t rem = static_cast<uint32_t>(row);
+            for (int d = outer.nd - 1; d >= 0; --d) {
+                uint32_t q, r;
+                outer.div[d].divmod(rem, q, r);
+                rem = q;
+#pragma unroll
+                for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * outer.strides[k][d];
+            }
+        }
+        const In0 *a = static_cast<const In0 *>(p.in[0]) + (F::NIN >= 1 ? off[0] : 0);
+        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
+        const In2 *c = static_cast<const In2 *>(p.in[2]) + (F::NIN >= 3 ? off[2] : 0);
+        Out *o = static_cast<Out *>(p.out) + off[NARR - 1];
+
+        In0 sa{};
+        In1 sb{};
+        In2 sc{};
+        if constexpr (F::NIN >= 1) { if (inner_bcast & 1u) sa = a[0]; }
+        if constexpr (F::NIN >= 2) { if (inner_bcast & 2u) sb = b[0]; }
+        if constexpr (F::NIN >= 3) { if (inner_bcast & 4u) sc = c[0]; }
+
+        const int64_t v0 = chunk * (int64_t(TX) * UNROLL) + tx;  // first vector index
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t j = (v0 + int64_t(u) * TX) * VEC;  // first element
+            if (j + VEC <= L) {
+                vec_t<In0, VEC> va;
+                vec_t<In1, VEC> vb;
+                vec_t<In2, VEC> vc;
+                if constexpr (F::NIN >= 1) { if (!(inner_bcast & 1u)) va = load_vec<vec_t<In0, VEC>>(a + j); }
+                if constexpr (F::NIN >= 2) { if (!(inner_bcast & 2u)) vb = load_vec<vec_t<In1, VEC>>(b + j); }
+                if constexpr (F::NIN >= 3) { if (!(inner_bcast & 4u)) vc = load_vec<vec_t<In2, VEC>>(c + j); }
+                vec_t<Out, VEC> r;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    In0 x = sa;
+                    In1 y = sb;
+                    In2 z = sc;
+                    if constexpr (F::NIN >= 1) { if (!(inner_bcast & 1u)) x = va.v[k]; }
+                    if constexpr (F::NIN >= 2) { if (!(inner_bcast & 2u)) y = vb.v[k]; }
+                    if constexpr (F::NIN >= 3) { if (!(inner_bcast & 4u)) z = vc.v[k]; }
+                    r.v[k] = ew_apply(f, x, y, z);
+                }
+                store_vec(o + j, r);
+            }
+            else {
+                for (int64_t e = j; e < L; ++e) {
+                    In0 x = sa;
+                    In1 y = sb;
+                    In2 z = sc;
+                    if constexpr (F::NIN >= 1) { if (!(inner_bcast & 1u)) x = a[e]; }
+                    if constexpr (F::NIN >= 2) { if (!(inner_bcast & 2u)) y = b[e]; }
+                    if constexpr (F::NIN >= 3) { if (!(inner_bcast & 4u)) z = c[e]; }
+                    o[e] = ew_apply(f, x, y, z);
+                }
+            }
+        }
+    }
+}
+
+// -------------------------------------------------------------- transpose
+// Dimensions: P (extent np) where the staged inputs are unit-stride, Q (extent
+// nq, the last collapsed dimension) where the output is unit-stride, and the
+// remaining `batch` dimensions.  A block handles one 32x32 (P x Q) tile of one
+// batch entry: staged inputs are read with threads running along P and parked
+// in shared memory, everything else is read with threads running along Q.
+constexpr int kTile = 32;
+constexpr int kTileRows = 8;  // block = 32 x 8 threads
+
+template <class F>
+__global__ void __launch_bounds__(kTile *kTileRows)
+    ew_transpose_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> batch, int64_t np, int64_t nq,
+                        int64_t sp0, int64_t sp1, int64_t sp2, int64_t spo, int64_t sq0, int64_t sq1,
+                        int64_t sq2, int64_t sqo, unsigned staged, int64_t tiles_p, int64_t tiles_q,
+                        int64_t nwork)
+{
+    using In0 = typename F::In0;
+    using In1 = typename F::In1;
+    using In2 = typename F::In2;
+    using Out = typename F::Out;
+    constexpr int NARR = F::NIN + 1;
+    __shared__ In0 s0[F::NIN >= 1 ? kTile : 1][kTile + 1];
+    __shared__ In1 s1[F::NIN >= 2 ? kTile : 1][kTile + 1];
+    __shared__ In2 s2[F::NIN >= 3 ? kTile : 1][kTile + 1];
+
+    const int tx = threadIdx.x & (kTile - 1);
+    const int ty = threadIdx.x / kTile;
+    const int64_t tiles_per_batch = tiles_p * tiles_q;
+
+    for (int64_t w = blockIdx.x; w < nwork; w += gridDim.x) {
+        const int64_t bi = w / tiles_per_batch;
+        const int64_t tw = w - bi * tiles_per_batch;
+        const int64_t tp = tw / tiles_q;
+        const int64_t tq = tw - tp * tiles_q;
+        const int64_t p0 = tp * kTile, q0 = tq * kTile;
+
+        int64_t off[NARR];
+#pragma unroll
+        for (int k = 0; k < NARR; ++k) off[k] = 0;
+        {
+            uint32_t rem = static_cast<uint32_t>(bi);
+            for (int d = batch.nd - 1; d >= 0; --d) {
+                uint32_t q, r;
+                batch.div[d].divmod(rem, q, r);
+                rem = q;
+#pragma unroll
+                for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * batch.strides[k][d];
+            }
+        }
+        const In0 *a = static_cast<const In0 *>(p.in[0]) + (F::NIN >= 1 ? off[0] : 0);
+        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
+        const In2 *c = static_cast<const In2 *>(p.in[2]) + (F::NIN >= 3 ? off[2] : 0);
+        Out *o = static_cast<Out *>(p.out) + off[NARR - 1];
+
+        // stage: threads run along P (tx), rows of the tile along Q (ty + 8r)
+        if (staged) {
+            const int64_t pp = p0 + tx;
+#pragma unroll
+            for (int r = 0; r < kTile / kTileRows; ++r) {
+                const int qi = ty + r * kTileRows;
+                const int64_t qq = q0 + qi;
+                if (pp < np && qq < nq) {
+                    if constexpr (F::NIN >= 1) { if (staged & 1u) s0[qi][tx] = a[pp * sp0 + qq * sq0]; }
+                    if constexpr (F::NIN >= 2) { if (staged & 2u) s1[qi][tx] = b[pp * sp1 + qq * sq1]; }
+                    if constexpr (F::NIN >= 3) { if (staged & 4u) s2[qi][tx] = c[pp * sp2 + qq * sq2]; }
+                }
+            }
+        }
+        __syncthreads();
+        // compute: threads run along Q (tx), rows of the tile along P (ty + 8r)
+        {
+            const int64_t qq = q0 + tx;
+#pragma unroll
+            for (int r = 0; r < kTile / kTileRows; ++r) {
+                const int pi = ty + r * kTileRows;
+                const int64_t pp = p0 + pi;
+                if (pp < np && qq < nq) {
+                    In0 x{};
+                    In1 y{};
+                    In2 z{};
+                    if constexpr (F::NIN >= 1) x = (staged & 1u) ? s0[tx][pi] : a[pp * sp0 + qq * sq0];
+                    if constexpr (F::NIN >= 2) y = (staged & 2u) ? s1[tx][pi] : b[pp * sp1 + qq * sq1];
+                    if constexpr (F::NIN >= 3) z = (staged & 4u) ? s2[tx][pi] : c[pp * sp2 + qq * sq2];
+                    o[pp * spo + qq * sqo] = ew_apply(f, x, y, z);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------- generic
+template <class F, bool IDX32, int UNROLL>
+__global__ void __launch_bounds__(kEwThreads)
+    ew_generic_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> m, int64_t n)
+{
+    using In0 = typename F::In0;
+    using In1 = typename F::In1;
+    using In2 = typename F::In2;
+    using Out = typename F::Out;
+    constexpr int NARR = F::NIN + 1;
+    const int64_t block_base = int64_t(blockIdx.x) * (kEwThreads * UNROLL);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t i = block_base + int64_t(u) * kEwThreads + threadIdx.x;
+        if (i >= n) break;
+        int64_t off[NARR];
+#pragma unroll
+        for (int k = 0; k < NARR; ++k) off[k] = 0;
+        if constexpr (IDX32) {
+            uint32_t rem = static_cast<uint32_t>(i);
+            for (int d = m.nd - 1; d > 0; --d) {
+                uint32_t q, r;
+                m.div[d].divmod(rem, q, r);
+                rem = q;
+#pragma unroll
+                for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * m.strides[k][d];
+            }
+#pragma unroll
+            for (int k = 0; k < NARR; ++k) off[k] += int64_t(rem) * m.strides[k][0];
+        }
+        else {
+            int64_t rem = i;
+            for (int d = m.nd - 1; d > 0; --d) {
+                const int64_t q = rem / m.shape[d];
+                const int64_t r = rem - q * m.shape[d];
+                rem = q;
+#pragma unroll
+                for (int k = 0; k < NARR; ++k) off[k] += r * m.strides[k][d];
+            }
+#pragma unroll
+            for (int k = 0; k < NARR; ++k) off[k] += rem * m.strides[k][0];
+        }
+        In0 x{};
+        In1 y{};
+        In2 z{};
+        if constexpr (F::NIN >= 1) x = static_cast<const In0 *>(p.in[0])[off[0]];
+        if constexpr (F::NIN >= 2) y = static_cast<const In1 *>(p.in[1])[off[1]];
+        if constexpr (F::NIN >= 3) z = static_cast<const In2 *>(p.in[2])[off[2]];
+        static_cast<Out *>(p.out)[off[NARR - 1]] = ew_apply(f, x, y, z);
+    }
+}
+
+// --------------------------------------------------------------- launcher
+
+template <int NARR>
+inline void fill_meta(StridedMeta<NARR> &m, const EwPlan &plan, const int *dims, int ndims,
+                      const int *arr_index)
+{
+    m.nd = ndims;
+    for (int i = 0; i < ndims; ++i) {
+        const int d = dims[i];
+        m.shape[i] = plan.shape[d];
+        m.div[i] = FastDiv32(static_cast<uint32_t>(plan.shape[d] > 0 && plan.shape[d] < (int64_t(1) << 31)
+                                                       ? plan.shape[d]
+                                                       : 1));
+        for (int k = 0; k < NARR; ++k) m.strides[k][i] = plan.strides[arr_index[k]][d];
+    }
+}
+
+inline int ew_grid(int64_t nwork)
+{
+    const int64_t cap = int64_t(device_props().sm_count) * tuning_ctas_per_sm();
+    return static_cast<int>(nwork < cap ? (nwork < 1 ? 1 : nwork) : cap);
+}
+
+// Launch functor F over the planned iteration space.  `in` holds F::NIN base
+// pointers and `out` the output pointer, all already displaced by the plan's
+// offsets.  The plan's array order is inputs first, output last.
+template <class F>
+int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, cudaStream_t stream)
+{
+    constexpr int NIN = F::NIN;
+    constexpr int NARR = NIN + 1;
+    using Out = typename F::Out;
+    if (plan.n == 0) return DPB_OK;
+    EwPtrs<F> p;
+    for (int k = 0; k < 3; ++k) p.in[k] = (k < NIN) ? in[k] : nullptr;
+    p.out = out;
+    int arr_index[NARR];
+    for (int k = 0; k < NARR; ++k) arr_index[k] = k;
+    const size_t in_sizes[3] = {sizeof(typename F::In0), sizeof(typename F::In1),
+                                sizeof(typename F::In2)};
+    constexpr int VEC = ew_vec_width<F>();
+
+    switch (plan.kind) {
+    case EW_CONTIG: {
+        bool aligned = is_aligned(out, sizeof(Out) * VEC);
+        for (int k = 0; k < NIN; ++k)
+            if (!(plan.bcast_mask & (1u << k))) aligned = aligned && is_aligned(in[k], in_sizes[k] * VEC);
+        if (aligned && VEC > 1) {
+            constexpr int UNROLL = 4;
+            const int64_t tiles = plan.n / (int64_t(kEwThreads) * VEC * UNROLL);
+            ew_contig_vec_kernel<F, VEC, UNROLL>
+                <<<ew_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
+            note_kernel("ew_contig_vec");
+        }
+        else {
+            constexpr int UNROLL = 4;
+            const int64_t tiles = plan.n / (int64_t(kEwThreads) * UNROLL);
+            ew_contig_vec_kernel<F, 1, UNROLL>
+                <<<ew_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
+            note_kernel("ew_contig_scalar");
+        }
+        return check_launch("ew_contig");
+    }
+    case EW_ROWS: {
+        const int last = plan.nd - 1;
+        const int64_t L = plan.shape[last];
+        int dims[kMaxD];
+        for (int i = 0; i < last; ++i) dims[i] = i;
+        StridedMeta<NARR> outer;
+        fill_meta(outer, plan, dims, last, arr_index);
+        int64_t nrows = 1;
+        for (int i = 0; i < last; ++i) nrows *= plan.shape[i];
+        unsigned inner_bcast = 0;
+        for (int k = 0; k < NIN; ++k)
+            if (plan.strides[k][last] == 0) inner_bcast |= (1u << k);
+        // 16-byte accesses need aligned row starts in every unit-stride operand
+        bool aligned = is_aligned(out, sizeof(Out) * VEC);
+        for (int i = 0; i < last; ++i) aligned = aligned && (plan.strides[NARR - 1][i] % VEC == 0);
+        for (int k = 0; k < NIN; ++k) {
+            if (inner_bcast & (1u << k)) continue;
+            aligned = aligned && is_aligned(in[k], in_sizes[k] * VEC);
+            for (int i = 0; i < last; ++i) aligned = aligned && (plan.strides[k][i] % VEC == 0);
+        }
+        const int vec = (aligned && VEC > 1) ? VEC : 1;
+        constexpr int UNROLL = 4;
+        const int64_t nvec = ceil_div(L, vec);
+        int tx_log2 = 0;
+        while ((1 << tx_log2) < kEwThreads && (int64_t(1) << tx_log2) * UNROLL < nvec) ++tx_log2;
+        const int TX = 1 << tx_log2, TY = kEwThreads >> tx_log2;
+        const int64_t chunks = ceil_div(nvec, int64_t(TX) * UNROLL);
+        const int64_t nwork = ceil_div(nrows, TY) * chunks;
+        if (vec > 1) {
+            ew_rows_kernel<F, VEC, UNROLL><<<ew_grid(nwork), kEwThreads, 0, stream>>>(
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork);
+            note_kernel("ew_rows_vec");
+        }
+        else {
+            ew_rows_kernel<F, 1, UNROLL><<<ew_grid(nwork), kEwThreads, 0, stream>>>(
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork);
+            note_kernel("ew_rows_scalar");
+        }
+        return check_launch("ew_rows");
+    }
+    case EW_TRANSPOSE: {
+        if constexpr (sizeof(typename F::In0) <= 8 && sizeof(typename F::In1) <= 8 &&
+                      sizeof(typename F::In2) <= 8) {
+            const int q = plan.nd - 1, pd = plan.tdim;
+            int dims[kMaxD];
+            int nb = 0;
+            int64_t nbatch = 1;
+            for (int i = 0; i < plan.nd; ++i)
+                if (i != q && i != pd) {
+                    dims[nb++] = i;
+                    nbatch *= plan.shape[i];
+                }
+            StridedMeta<NARR> batch;
+            fill_meta(batch, plan, dims, nb, arr_index);
+            const int64_t np = plan.shape[pd], nq = plan.shape[q];
+            const int64_t tiles_p = ceil_div(np, kTile), tiles_q = ceil_div(nq, kTile);
+            const int64_t nwork = nbatch * tiles_p * tiles_q;
+            auto sp = [&](int k) { return k < NIN ? plan.strides[k][pd] : 0; };
+            auto sq = [&](int k) { return k < NIN ? plan.strides[k][q] : 0; };
+            ew_transpose_kernel<F><<<ew_grid(nwork), kTile * kTileRows, 0, stream>>>(
+                f, p, batch, np, nq, sp(0), sp(1), sp(2), plan.strides[NARR - 1][pd], sq(0), sq(1),
+                sq(2), plan.strides[NARR - 1][q], plan.staged_mask, tiles_p, tiles_q, nwork);
+            note_kernel("ew_transpose");
+            return check_launch("ew_transpose");
+        }
+        // element types wider than 8 bytes are not staged: fall through
+    }
+    case EW_GENERIC:
+    default: {
+        int dims[kMaxD];
+        for (int i = 0; i < plan.nd; ++i) dims[i] = i;
+        StridedMeta<NARR> m;
+        fill_meta(m, plan, dims, plan.nd, arr_index);
+        constexpr int UNROLL = 4;
+        const int64_t nblocks = ceil_div(plan.n, int64_t(kEwThreads) * UNROLL);
+        if (nblocks > 0x7fffffffLL)
+            return set_error(DPB_ERR_RUNTIME, "iteration space too large for the strided kernel");
+        if (plan.n < (int64_t(1) << 31)) {
+            ew_generic_kernel<F, true, UNROLL>
+                <<<static_cast<unsigned>(nblocks), kEwThreads, 0, stream>>>(f, p, m, plan.n);
+            note_kernel("ew_generic32");
+        }
+        else {
+            ew_generic_kernel<F, false, UNROLL>
+                <<<static_cast<unsigned>(nblocks), kEwThreads, 0, stream>>>(f, p, m, plan.n);
+            note_kernel("ew_generic64");
+        }
+        return check_launch("ew_generic");
+    }
+    }
+}
+
+}  // namespace dpb

@@ -1,0 +1,168 @@
+// Reduction operators.  A reduction operator R describes
+//   R::In      element type read from memory
+//   R::Acc     accumulator type carried through the tree (also the type of
+//              the partial results between the two passes)
+//   R::Out     element type written to the result
+//   identity() neutral accumulator
+//   load(v, i) accumulator for element v found at reduction index i
+//   combine    associative, commutative merge of two accumulators
+//   finish     accumulator -> result element
+//   R::Stage2  the operator that merges partial accumulators (In = Acc)
+//
+// Semantics follow the reference: sums of bool into bool are logical-or
+// (source/reductions/sum.cpp:268-270), floating max/min propagate NaN
+// (include/utils/sycl_utils.hpp:332-376), argmax/argmin return the smallest
+// index among equal extremes and treat NaN as the extreme
+// (include/kernels/reductions.hpp:1917-1971,2062-2117; source/reductions/argmax.cpp:139-141),
+// identities as in sycl_utils.hpp:380-571.
+#pragma once
+
+#include <limits>
+
+#include "common.cuh"
+#include "ew_ops.cuh"
+
+namespace dpb {
+
+// accumulate half in float
+template <class Out> struct acc_of { using type = Out; };
+template <> struct acc_of<half_t> { using type = float; };
+template <class Out> using acc_of_t = typename acc_of<Out>::type;
+
+template <class T> DPB_HD T lowest_value()
+{
+    if constexpr (std::is_same_v<T, float>) return -INFINITY;
+    else if constexpr (std::is_same_v<T, double>) return -static_cast<double>(INFINITY);
+    else if constexpr (is_bool_v<T>) return bool_t(false);
+    else return std::numeric_limits<T>::lowest();
+}
+template <class T> DPB_HD T highest_value()
+{
+    if constexpr (std::is_same_v<T, float>) return INFINITY;
+    else if constexpr (std::is_same_v<T, double>) return static_cast<double>(INFINITY);
+    else if constexpr (is_bool_v<T>) return bool_t(true);
+    else return std::numeric_limits<T>::max();
+}
+
+// ----------------------------------------------------------- sum and prod
+template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct SumRed {
+    using In = TIn;
+    using Acc = TAcc;
+    using Out = TOut;
+    using Stage2 = SumRed<Acc, TOut, Acc>;
+    static DPB_D Acc identity()
+    {
+        if constexpr (is_cplx_v<Acc>) return Acc(0, 0);
+        else if constexpr (is_bool_v<Acc>) return bool_t(false);
+        else return Acc(0);
+    }
+    static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc combine(Acc a, Acc b)
+    {
+        if constexpr (is_bool_v<Acc>) return bool_t(a.v || b.v);
+        else if constexpr (is_cplx_v<Acc>) return Acc(a.re + b.re, a.im + b.im);
+        else return static_cast<Acc>(a + b);
+    }
+    static DPB_D Out finish(Acc a) { return convert<Out>(a); }
+};
+
+template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ProdRed {
+    using In = TIn;
+    using Acc = TAcc;
+    using Out = TOut;
+    using Stage2 = ProdRed<Acc, TOut, Acc>;
+    static DPB_D Acc identity()
+    {
+        if constexpr (is_cplx_v<Acc>) return Acc(1, 0);
+        else if constexpr (is_bool_v<Acc>) return bool_t(true);
+        else return Acc(1);
+    }
+    static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc combine(Acc a, Acc b)
+    {
+        if constexpr (is_bool_v<Acc>) return bool_t(a.v && b.v);
+        else if constexpr (is_cplx_v<Acc>)
+            return Acc(a.re * b.re - a.im * b.im, a.re * b.im + a.im * b.re);
+        else return static_cast<Acc>(a * b);
+    }
+    static DPB_D Out finish(Acc a) { return convert<Out>(a); }
+};
+
+// ------------------------------------------------------------ max and min
+template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ExtremeRed {
+    using In = TIn;
+    using Acc = TAcc;
+    using Out = TOut;
+    using Stage2 = ExtremeRed<IS_MAX, Acc, TOut, Acc>;
+    static DPB_D Acc identity() { return IS_MAX ? lowest_value<Acc>() : highest_value<Acc>(); }
+    static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc combine(Acc a, Acc b)
+    {
+        if constexpr (is_bool_v<Acc>) return IS_MAX ? bool_t(a.v || b.v) : bool_t(a.v && b.v);
+        else if constexpr (std::is_floating_point_v<Acc>) {
+            if (a != a) return a;
+            if (b != b) return b;
+            return IS_MAX ? (a > b ? a : b) : (a < b ? a : b);
+        }
+        else return IS_MAX ? (a > b ? a : b) : (a < b ? a : b);
+    }
+    static DPB_D Out finish(Acc a) { return convert<Out>(a); }
+};
+
+// ------------------------------------------------------ argmax and argmin
+template <class V> struct alignas(16) ValIdx {
+    V val;
+    int64_t idx;
+};
+
+// Total order used by the search: NaN beats every number; among equals (and
+// among NaNs) the smaller index wins.
+template <bool IS_MAX, class V> DPB_D bool search_better(const ValIdx<V> &a, const ValIdx<V> &b)
+{
+    if constexpr (std::is_floating_point_v<V>) {
+        const bool an = a.val != a.val, bn = b.val != b.val;
+        if (an || bn) {
+            if (an && bn) return a.idx < b.idx;
+            return an;
+        }
+    }
+    if (a.val == b.val) return a.idx < b.idx;
+    return IS_MAX ? (a.val > b.val) : (a.val < b.val);
+}
+
+template <class V> struct search_val { using type = V; };
+template <> struct search_val<half_t> { using type = float; };
+template <> struct search_val<bool_t> { using type = uint8_t; };
+
+template <bool IS_MAX, class TIn, class V = typename search_val<TIn>::type, bool STAGE2 = false>
+struct SearchRed {
+    using In = std::conditional_t<STAGE2, ValIdx<V>, TIn>;
+    using Acc = ValIdx<V>;
+    using Out = int64_t;
+    using Stage2 = SearchRed<IS_MAX, TIn, V, true>;
+    // The identity carries the largest index so that any real element wins a tie.
+    static DPB_D Acc identity()
+    {
+        Acc a;
+        a.val = IS_MAX ? lowest_value<V>() : highest_value<V>();
+        a.idx = std::numeric_limits<int64_t>::max();
+        return a;
+    }
+    static DPB_D Acc load(const In &v, int64_t i)
+    {
+        if constexpr (STAGE2) {
+            return v;
+        }
+        else {
+            Acc a;
+            if constexpr (is_bool_v<TIn>) a.val = v.v ? 1 : 0;
+            else a.val = convert<V>(v);
+            a.idx = i;
+            return a;
+        }
+    }
+    static DPB_D Acc combine(const Acc &a, const Acc &b) { return search_better<IS_MAX>(a, b) ? a : b; }
+    static DPB_D Out finish(const Acc &a) { return a.idx; }
+};
+
+}  // namespace dpb

@@ -1,0 +1,422 @@
+/*
+ * dpnp_b200.h -- C ABI of libdpnp_b200.so: the sm_100a data-parallel core
+ * (strided elementwise engine + reduction-over-axis engine) that sits where
+ * dpnp's pybind11 modules _tensor_impl / _tensor_elementwise_impl /
+ * _tensor_reductions_impl sit in the reference.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; every device pointer is a CUDA device
+ *    address valid on the device that is current in the calling thread;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *    stream); all work is enqueued, nothing synchronises unless stated;
+ *  - strides and offsets are in ELEMENTS, not bytes (as in usm_ndarray,
+ *    dpnp/tensor/_usmarray.pxd:81-111);
+ *  - every function returns a dpb_status; on failure a thread-local message
+ *    is available from dpb_last_error().  No exception crosses this boundary;
+ *  - there is no CPU fallback: without a CUDA device every compute entry
+ *    point fails with DPB_ERR_CUDA.
+ *
+ * Each declaration cites the reference interface it replaces as
+ * file:line relative to the root of IntelPython/dpnp.
+ */
+#ifndef DPNP_B200_H
+#define DPNP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ types */
+
+/* Type ids, same order as typenum_t in
+ * dpnp/tensor/libtensor/include/utils/type_dispatch_building.hpp:45-62 */
+typedef enum dpb_typenum {
+    DPB_BOOL = 0,
+    DPB_INT8 = 1,
+    DPB_UINT8 = 2,
+    DPB_INT16 = 3,
+    DPB_UINT16 = 4,
+    DPB_INT32 = 5,
+    DPB_UINT32 = 6,
+    DPB_INT64 = 7,
+    DPB_UINT64 = 8,
+    DPB_HALF = 9,
+    DPB_FLOAT = 10,
+    DPB_DOUBLE = 11,
+    DPB_CFLOAT = 12,
+    DPB_CDOUBLE = 13,
+    DPB_NUM_TYPES = 14
+} dpb_typenum;
+
+/* Status codes.  The Python shim maps VALUE->ValueError, RUNTIME and CUDA->
+ * RuntimeError, MEMORY->MemoryError, TYPE->TypeError, matching the exception
+ * classes thrown by the reference dispatchers
+ * (dpnp/tensor/libtensor/source/elementwise_functions/elementwise_functions.hpp:96-164). */
+typedef enum dpb_status {
+    DPB_OK = 0,
+    DPB_ERR_VALUE = 1,
+    DPB_ERR_RUNTIME = 2,
+    DPB_ERR_CUDA = 3,
+    DPB_ERR_MEMORY = 4,
+    DPB_ERR_TYPE = 5
+} dpb_status;
+
+/* Contiguity / writability flags, values as in
+ * dpnp/include/usm_ndarray_constants.h:32-59 */
+#define DPB_FLAG_C_CONTIGUOUS 1
+#define DPB_FLAG_F_CONTIGUOUS 2
+#define DPB_FLAG_WRITABLE 4
+
+/* Largest number of dimensions an array descriptor may carry, and the largest
+ * number that may remain after the iteration space has been collapsed (the
+ * collapsed shape and strides travel by value in kernel parameters). */
+#define DPB_MAX_ND 32
+#define DPB_MAX_COLLAPSED_ND 10
+
+/* Plain-C view of an array: what dpnp4pybind11.hpp's `class usm_ndarray`
+ * (dpnp/include/dpnp4pybind11.hpp:341-621) exposes to the C++ dispatchers. */
+typedef struct dpb_array {
+    void *data;             /* device address of element [0,...,0]            */
+    int32_t nd;             /* number of dimensions, 0..DPB_MAX_ND            */
+    int32_t typenum;        /* dpb_typenum                                    */
+    int32_t flags;          /* DPB_FLAG_* bits                                */
+    int32_t device;         /* CUDA device ordinal that owns `data`           */
+    const int64_t *shape;   /* nd extents (host memory)                       */
+    const int64_t *strides; /* nd strides in elements (host memory); NULL
+                               means C-contiguous                             */
+} dpb_array;
+
+/* ------------------------------------------------------------- operations */
+
+/* Unary elementwise operations (one header each under
+ * dpnp/tensor/libtensor/include/kernels/elementwise_functions/). */
+typedef enum dpb_unary_op {
+    DPB_U_NEGATIVE = 0, /* negative.hpp */
+    DPB_U_POSITIVE,     /* positive.hpp */
+    DPB_U_ABS,          /* abs.hpp */
+    DPB_U_EXP,          /* exp.hpp:63-133 */
+    DPB_U_LOG,          /* log.hpp:60-84 */
+    DPB_U_SQRT,         /* sqrt.hpp:62-84 */
+    DPB_U_ERF,          /* dpnp/backend/kernels/elementwise_functions/erf.hpp:51-99 */
+    DPB_U_SQUARE,       /* square.hpp */
+    DPB_U_RECIPROCAL,   /* reciprocal.hpp */
+    DPB_U_SIN,          /* sin.hpp */
+    DPB_U_COS,          /* cos.hpp */
+    DPB_U_TANH,         /* tanh.hpp */
+    DPB_U_EXPM1,        /* expm1.hpp */
+    DPB_U_LOG1P,        /* log1p.hpp */
+    DPB_U_FLOOR,        /* floor.hpp */
+    DPB_U_CEIL,         /* ceil.hpp */
+    DPB_U_SIGN,         /* sign.hpp */
+    DPB_U_LOGICAL_NOT,  /* logical_not.hpp */
+    DPB_U_ISNAN,        /* isnan.hpp */
+    DPB_U_ISFINITE,     /* isfinite.hpp */
+    DPB_U_ISINF,        /* isinf.hpp */
+    DPB_U_NUM_OPS
+} dpb_unary_op;
+
+/* Binary elementwise operations. */
+typedef enum dpb_binary_op {
+    DPB_B_ADD = 0,       /* add.hpp:62-114 */
+    DPB_B_SUBTRACT,      /* subtract.hpp */
+    DPB_B_MULTIPLY,      /* multiply.hpp:62-105 */
+    DPB_B_TRUE_DIVIDE,   /* true_divide.hpp:62-113 */
+    DPB_B_MAXIMUM,       /* maximum.hpp */
+    DPB_B_MINIMUM,       /* minimum.hpp */
+    DPB_B_EQUAL,         /* equal.hpp */
+    DPB_B_NOT_EQUAL,     /* not_equal.hpp */
+    DPB_B_LESS,          /* less.hpp:60-101 */
+    DPB_B_LESS_EQUAL,    /* less_equal.hpp */
+    DPB_B_GREATER,       /* greater.hpp */
+    DPB_B_GREATER_EQUAL, /* greater_equal.hpp */
+    DPB_B_LOGICAL_AND,   /* logical_and.hpp */
+    DPB_B_LOGICAL_OR,    /* logical_or.hpp */
+    DPB_B_POW,           /* pow.hpp */
+    DPB_B_NUM_OPS
+} dpb_binary_op;
+
+/* Reductions over trailing axes. */
+typedef enum dpb_reduce_op {
+    DPB_R_SUM = 0, /* source/reductions/sum.cpp */
+    DPB_R_PROD,    /* source/reductions/prod.cpp */
+    DPB_R_MAX,     /* source/reductions/max.cpp (NaN-propagating for fp) */
+    DPB_R_MIN,     /* source/reductions/min.cpp */
+    DPB_R_NUM_OPS
+} dpb_reduce_op;
+
+/* Search reductions (index of the first extreme value, NaN counts as extreme). */
+typedef enum dpb_search_op {
+    DPB_S_ARGMAX = 0, /* source/reductions/argmax.cpp:76-141 */
+    DPB_S_ARGMIN,     /* source/reductions/argmin.cpp */
+    DPB_S_NUM_OPS
+} dpb_search_op;
+
+/* -------------------------------------------------- errors and the device */
+
+/* Message of the last failure in the calling thread ("" if none). */
+const char *dpb_last_error(void);
+
+/* Library version string. */
+const char *dpb_version(void);
+
+/* Number of CUDA devices visible (0 without a driver/GPU; never fails). */
+int dpb_device_count(void);
+
+/* Make `device` current in the calling thread (cudaSetDevice). Replaces the
+ * device selection implied by a SyclQueue (dpnp/tensor/_compute_follows_data.pyx:67-160). */
+int dpb_set_device(int device);
+int dpb_get_device(int *device);
+
+/* SM count and total global memory of `device`. */
+int dpb_device_info(int device, int *sm_count, size_t *total_mem, int *cc_major, int *cc_minor);
+
+/* ---------------------------------------------------------------- streams */
+/* A cudaStream_t stands where the reference passes `sycl::queue` plus a
+ * `depends` event list (dpnp/tensor/_elementwise_common.py:692-700); work on
+ * one stream is ordered, which is what SequentialOrderManager guarantees. */
+
+int dpb_stream_create(void **stream);
+int dpb_stream_destroy(void *stream);
+int dpb_stream_synchronize(void *stream);
+int dpb_device_synchronize(void);
+
+/* CUDA events, used for timing by the measurement harness. */
+int dpb_event_create(void **event);
+int dpb_event_destroy(void *event);
+int dpb_event_record(void *event, void *stream);
+int dpb_event_synchronize(void *event);
+int dpb_event_elapsed_ms(void *start, void *stop, float *ms);
+
+/* ------------------------------------------------------------- allocator */
+/* Stream-ordered pool (cudaMallocAsync on the device's default mempool with a
+ * raised release threshold).  Replaces dpctl.memory.MemoryUSMDevice as used by
+ * dpnp/tensor/_usmarray.pyx:440-448 and sycl::malloc_device for temporaries
+ * (dpnp/tensor/libtensor/include/utils/sycl_alloc_utils.hpp:107-130).
+ * Returned addresses are at least 256-byte aligned.  A zero-byte request
+ * returns a unique non-NULL address. */
+
+int dpb_malloc(size_t nbytes, void *stream, void **ptr);
+/* Free is ordered after all work already enqueued on `stream`; this is what
+ * keep_args_alive / async_smart_free achieve with host tasks in the reference
+ * (dpnp/include/dpnp4pybind11.hpp:670-736; sycl_alloc_utils.hpp:185-222). */
+int dpb_free(void *ptr, void *stream);
+/* Release cached memory back to the driver down to `keep_bytes`. */
+int dpb_pool_trim(size_t keep_bytes);
+/* Pool counters of the current device: bytes reserved from the driver and
+ * bytes handed out, now and at the high-water mark. */
+int dpb_pool_stats(size_t *reserved, size_t *used, size_t *reserved_high, size_t *used_high);
+/* Optional cap on live bytes handed out by dpb_malloc (0 = no cap); a request
+ * that would exceed it fails with DPB_ERR_MEMORY without touching the device.
+ * Used to exercise out-of-memory handling from the host. */
+int dpb_pool_set_limit(size_t max_live_bytes);
+
+/* Pinned host memory for staging (cudaHostAlloc / cudaFreeHost). */
+int dpb_host_alloc(size_t nbytes, void **ptr);
+int dpb_host_free(void *ptr);
+
+/* Raw copies; kind: 0 host->device, 1 device->host, 2 device->device.
+ * Replaces the memcpy fast path of copy_usm_ndarray_into_usm_ndarray
+ * (dpnp/tensor/libtensor/source/copy_and_cast_usm_to_usm.cpp:147-166) and the
+ * host<->USM copies of dpnp/tensor/libtensor/source/copy_numpy_ndarray_into_usm_ndarray.cpp. */
+int dpb_memcpy(void *dst, const void *src, size_t nbytes, int kind, void *stream);
+/* Byte-wise memset. */
+int dpb_memset(void *dst, int value, size_t nbytes, void *stream);
+
+/* ----------------------------------------- iteration-space simplification */
+/* Collapse an iteration space shared by `narrays` (1..4) arrays: dimensions
+ * are sorted by decreasing |stride| (the LAST array's strides are the primary
+ * key), dimensions whose strides are non-positive in every array and negative
+ * in at least one are reversed (offsets absorb the shift), and neighbouring
+ * dimensions whose strides chain in every array are merged.
+ *   shape   : in/out, nd extents
+ *   strides : in/out, narrays*nd values laid out [array][dim]
+ *   offsets : out, narrays element offsets to add to the base pointers
+ * Returns the new number of dimensions in *nd_out.
+ * Replaces simplify_iteration_space_1/_/3/_4
+ * (dpnp/tensor/libtensor/source/simplify_iteration_space.cpp:51-264) and
+ * simplify_iteration_{stride,two_strides,three_strides,four_strides}
+ * (dpnp/tensor/libtensor/include/utils/strided_iters.hpp:363-899). */
+int dpb_simplify_iteration_space(int narrays, int nd, int64_t *shape, int64_t *strides,
+                                 int64_t *offsets, int *nd_out);
+
+/* Order-preserving merge of neighbouring dimensions of one array
+ * (strided_iters.hpp:945-983, compact_iteration). */
+int dpb_compact_iteration(int nd, int64_t *shape, int64_t *strides, int *nd_out);
+
+/* True (1) if the byte ranges spanned by the two arrays intersect
+ * (dpnp/tensor/libtensor/include/utils/memory_overlap.hpp:52-107). */
+int dpb_array_overlap(const dpb_array *a, const dpb_array *b, int *overlap);
+/* True (1) if both arrays have the same pointer, type, shape and strides
+ * (memory_overlap.hpp:109-151). */
+int dpb_same_logical_tensors(const dpb_array *a, const dpb_array *b, int *same);
+
+/* ------------------------------------------------------ kernel-level ABI  */
+/* These take raw pointers plus element offsets, as the reference's kernel
+ * function-pointer types do (typeless pointer + offset).  `shape_strides` is a
+ * HOST array laid out [shape | strides of arg 1 | ... | strides of result],
+ * each nd long; it is copied into kernel parameters (the reference packs it
+ * into a device buffer per call, include/utils/offset_utils.hpp:93-135). */
+
+/* out[i] = op(in[i]); replaces unary_contig_impl_fn_ptr_t
+ * (include/kernels/elementwise_functions/common.hpp:693-700). */
+int dpb_unary_contig(int op, int t_in, int t_out, int64_t nelems, const void *in, int64_t in_off,
+                     void *out, int64_t out_off, void *stream);
+/* replaces unary_strided_impl_fn_ptr_t (common.hpp:702-713). */
+int dpb_unary_strided(int op, int t_in, int t_out, int64_t nelems, int nd,
+                      const int64_t *shape_strides, const void *in, int64_t in_off, void *out,
+                      int64_t out_off, void *stream);
+/* out[i] = op(a[i], b[i]); replaces binary_contig_impl_fn_ptr_t (common.hpp:715-727). */
+int dpb_binary_contig(int op, int t_a, int t_b, int t_out, int64_t nelems, const void *a,
+                      int64_t a_off, const void *b, int64_t b_off, void *out, int64_t out_off,
+                      void *stream);
+/* replaces binary_strided_impl_fn_ptr_t (common.hpp:729-744). */
+int dpb_binary_strided(int op, int t_a, int t_b, int t_out, int64_t nelems, int nd,
+                       const int64_t *shape_strides, const void *a, int64_t a_off, const void *b,
+                       int64_t b_off, void *out, int64_t out_off, void *stream);
+/* lhs[i] = op(lhs[i], rhs[i]); replaces binary_inplace_{contig,strided}_impl_fn_ptr_t
+ * (include/kernels/elementwise_functions/common_inplace.hpp). `shape_strides`
+ * is [shape | rhs strides | lhs strides]. */
+int dpb_binary_inplace_contig(int op, int t_rhs, int t_lhs, int64_t nelems, const void *rhs,
+                              int64_t rhs_off, void *lhs, int64_t lhs_off, void *stream);
+int dpb_binary_inplace_strided(int op, int t_rhs, int t_lhs, int64_t nelems, int nd,
+                               const int64_t *shape_strides, const void *rhs, int64_t rhs_off,
+                               void *lhs, int64_t lhs_off, void *stream);
+/* dst[i] = cond[i] ? x1[i] : x2[i]; replaces where_contig_impl_fn_ptr_t and
+ * where_strided_impl_fn_ptr_t (include/kernels/where.hpp:163-170,264-277).
+ * `shape_strides` is [shape | cond | x1 | x2 | dst]. */
+int dpb_where_contig(int t_cond, int t_val, int64_t nelems, const void *cond, const void *x1,
+                     const void *x2, void *dst, void *stream);
+int dpb_where_strided(int t_cond, int t_val, int64_t nelems, int nd, const int64_t *shape_strides,
+                      const void *cond, int64_t cond_off, const void *x1, int64_t x1_off,
+                      const void *x2, int64_t x2_off, void *dst, int64_t dst_off, void *stream);
+/* dst[i] = (T_dst) src[i]; replaces copy_and_cast_contig_fn_ptr_t /
+ * copy_and_cast_generic_fn_ptr_t (include/kernels/copy_and_cast.hpp:90-208,225-389). */
+int dpb_copy_cast_contig(int t_src, int t_dst, int64_t nelems, const void *src, int64_t src_off,
+                         void *dst, int64_t dst_off, void *stream);
+int dpb_copy_cast_strided(int t_src, int t_dst, int64_t nelems, int nd,
+                          const int64_t *shape_strides, const void *src, int64_t src_off, void *dst,
+                          int64_t dst_off, void *stream);
+
+/* Reduction of a C-contiguous (iter_nelems x reduction_nelems) matrix along
+ * its rows: res[i] = reduce_j arg[i*reduction_nelems + j].  Replaces
+ * reduction_contig_impl_fn_ptr of reduction_axis1_over_group_{temps,with_atomics}_contig_impl
+ * (include/kernels/reductions.hpp:859-958,1396-1624).  Deterministic: the
+ * partition of the work depends only on the sizes. */
+int dpb_reduce_axis1_contig(int op, int t_in, int t_out, int64_t iter_nelems,
+                            int64_t reduction_nelems, const void *arg, int64_t arg_off, void *res,
+                            int64_t res_off, void *stream);
+/* Reduction along the rows' index of a C-contiguous (reduction_nelems x
+ * iter_nelems) matrix: res[j] = reduce_i arg[i*iter_nelems + j].  Replaces
+ * reduction_axis0_over_group_{temps,with_atomics}_contig_impl (reductions.hpp:961-1046,1626-1856). */
+int dpb_reduce_axis0_contig(int op, int t_in, int t_out, int64_t iter_nelems,
+                            int64_t reduction_nelems, const void *arg, int64_t arg_off, void *res,
+                            int64_t res_off, void *stream);
+/* General case.  iter_shape_strides = [shape | arg strides | res strides]
+ * (iter_nd each); red_shape_strides = [shape | arg strides] (red_nd each).
+ * Replaces reduction_strided_impl_fn_ptr (reductions.hpp:740-753,1137-1394). */
+int dpb_reduce_strided(int op, int t_in, int t_out, int64_t iter_nelems, int64_t reduction_nelems,
+                       const void *arg, void *res, int iter_nd, const int64_t *iter_shape_strides,
+                       int64_t iter_arg_off, int64_t iter_res_off, int red_nd,
+                       const int64_t *red_shape_strides, int64_t red_arg_off, void *stream);
+/* Search reductions; result type is always int64, the index is the C-order
+ * position inside the reduced sub-space, ties resolve to the smallest index
+ * and a NaN is an extreme value.  Replaces search_axis1/axis0_over_group_temps_contig_impl
+ * and search_over_group_temps_strided_impl (reductions.hpp:2487-3308). */
+int dpb_search_axis1_contig(int op, int t_in, int64_t iter_nelems, int64_t reduction_nelems,
+                            const void *arg, int64_t arg_off, void *res, int64_t res_off,
+                            void *stream);
+int dpb_search_axis0_contig(int op, int t_in, int64_t iter_nelems, int64_t reduction_nelems,
+                            const void *arg, int64_t arg_off, void *res, int64_t res_off,
+                            void *stream);
+int dpb_search_strided(int op, int t_in, int64_t iter_nelems, int64_t reduction_nelems,
+                       const void *arg, void *res, int iter_nd, const int64_t *iter_shape_strides,
+                       int64_t iter_arg_off, int64_t iter_res_off, int red_nd,
+                       const int64_t *red_shape_strides, int64_t red_arg_off, void *stream);
+
+/* ---------------------------------------------------- dispatch-level ABI  */
+/* These take array descriptors, validate them and choose the kernel, as the
+ * reference's pybind11 dispatchers do.  Error conditions and messages follow
+ * the reference (ValueError for type/shape/overlap/read-only/ample-memory
+ * problems, RuntimeError for an unsupported type combination). */
+
+/* Result type of op for the given argument types, or -1 if unsupported.
+ * Replaces py_unary_ufunc_result_type / py_binary_ufunc_result_type
+ * (source/elementwise_functions/elementwise_functions.hpp:255-285,566-603). */
+int dpb_unary_result_type(int op, int t_in);
+int dpb_binary_result_type(int op, int t_a, int t_b);
+
+/* dst = op(src).  Replaces py_unary_ufunc (elementwise_functions.hpp:76-251). */
+int dpb_unary_ufunc(int op, const dpb_array *src, const dpb_array *dst, void *stream);
+/* dst = op(src1, src2).  Replaces py_binary_ufunc (elementwise_functions.hpp:305-563). */
+int dpb_binary_ufunc(int op, const dpb_array *src1, const dpb_array *src2, const dpb_array *dst,
+                     void *stream);
+/* lhs = op(lhs, rhs).  Replaces py_binary_inplace_ufunc (elementwise_functions.hpp:611-804). */
+int dpb_binary_inplace_ufunc(int op, const dpb_array *lhs, const dpb_array *rhs, void *stream);
+/* dst = cond ? x1 : x2.  Replaces py_where (source/where.cpp:73-245). */
+int dpb_where(const dpb_array *cond, const dpb_array *x1, const dpb_array *x2, const dpb_array *dst,
+              void *stream);
+/* dst[...] = cast(src[...]).  Replaces copy_usm_ndarray_into_usm_ndarray
+ * (source/copy_and_cast_usm_to_usm.cpp:76-...). */
+int dpb_copy_array_into_array(const dpb_array *src, const dpb_array *dst, void *stream);
+/* dst = src / scalar, in the type of dst.  Replaces _divide_by_scalar
+ * (source/elementwise_functions/true_divide.cpp:189-246,494). */
+int dpb_divide_by_scalar(const dpb_array *src, double scalar, const dpb_array *dst, void *stream);
+/* Fill with a scalar given as its bit pattern in the array's type (up to 16
+ * bytes).  Replaces _full_usm_ndarray / _zeros_usm_ndarray (source/full_ctor.cpp, zeros_ctor.cpp). */
+int dpb_full_array(const dpb_array *dst, const void *scalar_bits, void *stream);
+
+/* Whether op has a kernel for the (input, output) type pair.  Replaces
+ * _sum_over_axis_dtype_supported etc. (source/reductions/reduction_over_axis.hpp:72-134).
+ * The set is a subset of the reference's (same results; unsupported pairs are
+ * cast to a temporary by the caller, dpnp/tensor/_reduction.py:250-290). */
+int dpb_reduce_dtype_supported(int op, int t_in, int t_out);
+/* dst = reduce(src) over the last `trailing_dims_to_reduce` axes of src; the
+ * caller has permuted the reduced axes to the end and dst has the shape of
+ * the leading axes.  Replaces py_reduction_over_axis / py_tree_reduction_over_axis
+ * (reduction_over_axis.hpp:173-501,507-777). */
+int dpb_reduction_over_axis(int op, const dpb_array *src, int trailing_dims_to_reduce,
+                            const dpb_array *dst, void *stream);
+/* Replaces py_search_over_axis (reduction_over_axis.hpp:780-1047). */
+int dpb_search_over_axis(int op, const dpb_array *src, int trailing_dims_to_reduce,
+                         const dpb_array *dst, void *stream);
+
+/* ------------------------------------------------- fused expression paths */
+/* Black-Scholes call/put for n options in one pass (3 loads, 2 stores per
+ * option): the expression chain of examples/example_bs.py:50-75 with every
+ * intermediate rounded exactly as the op-by-op chain rounds it, so the result
+ * is bit-identical to running the chain through dpb_*_ufunc.  The reference
+ * has no fused path (26 ufunc launches + 2 copies). */
+int dpb_black_scholes_f64(int64_t n, const double *price, const double *strike, const double *t,
+                          double rate, double vol, double *call, double *put, void *stream);
+
+/* ------------------------------------------------------- device-side fill */
+/* Counter-based uniform generator: element i of the output depends only on
+ * (seed, i), so any shard of an array can be produced independently.
+ * Floating types get lo + (hi-lo)*u with u in [0,1); integer types get
+ * uniformly distributed integers in [lo, hi).  Stands in for the device-side
+ * generation of dpnp.random.uniform (dpnp/random/dpnp_iface_random.py:1965-2033),
+ * whose oneMKL streams are not reproducible elsewhere either. */
+int dpb_random_uniform(int typenum, void *dst, int64_t nelems, double lo, double hi, uint64_t seed,
+                       uint64_t first_index, void *stream);
+/* Standard normal variates (Box-Muller on the same counter-based stream). */
+int dpb_random_normal(int typenum, void *dst, int64_t nelems, double mean, double stddev,
+                      uint64_t seed, uint64_t first_index, void *stream);
+
+/* --------------------------------------------------------- introspection  */
+/* Name of the kernel family chosen by the most recent dispatch-level call in
+ * this thread ("binary_contig_vec", "strided_rows", "transpose_tile", ...),
+ * and the number of kernel launches issued by this thread since the last
+ * dpb_reset_launch_count(). */
+const char *dpb_last_kernel(void);
+int64_t dpb_launch_count(void);
+void dpb_reset_launch_count(void);
+/* Tuning knob: key "ctas_per_sm" etc.; returns DPB_ERR_VALUE for unknown keys. */
+int dpb_set_tuning(const char *key, int64_t value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DPNP_B200_H */
