@@ -1,0 +1,45 @@
+"""dpnp_b200: the data-parallel core of dpnp (strided elementwise engine and
+reduction-over-axis engine) on NVIDIA B200, behind the dpnp Python API.
+
+``import dpnp_b200 as np`` gives the subset of the dpnp namespace that the
+elementwise and reduction paths need: ``ndarray``, creation and view functions,
+the ufunc objects (add, subtract, multiply, divide, negative, exp, log, sqrt,
+erf, comparisons, ...), ``where``, and the reductions sum, prod, mean, max, min,
+argmax, argmin.  All compute runs in hand-written CUDA kernels of
+``libdpnp_b200.so``; there is no CPU fallback.
+"""
+
+import numpy as _np
+
+from . import _lib, memory, random, scipy, tensor
+from ._iface import (amax, amin, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
+                     asnumpy, astype, broadcast_to, check_limitations, copy, copyto,
+                     default_float_type, empty, empty_like, expand_dims, full, full_like,
+                     get_result_array, get_usm_ndarray, get_usm_ndarray_or_scalar,
+                     is_supported_array_type, max, mean, min, ones, ones_like, prod, ravel, reshape,
+                     squeeze, sum, transpose, where, zeros, zeros_like)
+from ._ufuncs import (DPNPBinaryFunc, DPNPUnaryFunc, abs, absolute, add, ceil, cos, divide, equal, erf,
+                      exp, expm1, floor, greater, greater_equal, isfinite, isinf, isnan, less,
+                      less_equal, log, log1p, logical_and, logical_not, logical_or, maximum, minimum,
+                      multiply, negative, not_equal, positive, power, reciprocal, sign, sin, sqrt,
+                      square, subtract, tanh, true_divide)
+from .dpnp_array import dpnp_array
+from .dpnp_array import dpnp_array as ndarray
+from .memory import ExecutionPlacementError, StreamQueue, get_default_queue
+
+__version__ = "0.1.0"
+
+# data types (dpnp/__init__.py:78-116)
+bool = bool_ = _np.bool_
+int8, int16, int32, int64 = _np.int8, _np.int16, _np.int32, _np.int64
+uint8, uint16, uint32, uint64 = _np.uint8, _np.uint16, _np.uint32, _np.uint64
+float16, float32, float64 = _np.float16, _np.float32, _np.float64
+complex64, complex128 = _np.complex64, _np.complex128
+intp = _np.intp
+dtype = _np.dtype
+finfo, iinfo = _np.finfo, _np.iinfo
+nan, inf, pi, e, newaxis = _np.nan, _np.inf, _np.pi, _np.e, None
+
+
+def isscalar(x):
+    return _np.isscalar(x)

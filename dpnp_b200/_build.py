@@ -9,6 +9,7 @@ statically, so the library needs only the driver at run time.
 from __future__ import annotations
 
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -46,12 +47,23 @@ def _sources() -> list[str]:
     )
 
 
-def _headers_mtime() -> float:
-    newest = 0.0
-    for root in (CSRC, os.path.join(HERE, os.pardir, "include")):
-        for f in os.listdir(root):
-            if f.endswith((".h", ".cuh", ".hpp")):
-                newest = max(newest, os.path.getmtime(os.path.join(root, f)))
+_INCLUDE_RE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _deps_mtime(path: str, seen: dict[str, float] | None = None) -> float:
+    """Newest modification time of `path` and of every header it includes."""
+    seen = {} if seen is None else seen
+    path = os.path.normpath(path)
+    if path in seen:
+        return seen[path]
+    seen[path] = newest = os.path.getmtime(path)
+    with open(path, "r", encoding="utf-8") as fh:
+        text = fh.read()
+    for inc in _INCLUDE_RE.findall(text):
+        cand = os.path.normpath(os.path.join(os.path.dirname(path), inc))
+        if os.path.exists(cand):
+            newest = max(newest, _deps_mtime(cand, seen))
+    seen[path] = newest
     return newest
 
 
@@ -66,7 +78,6 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None,
     """Compile and link the library; returns its path."""
     nvcc = _nvcc()
     os.makedirs(OBJ_DIR, exist_ok=True)
-    hdr_time = _headers_mtime()
     extra = ["-Xptxas", "-v"] if ptxas_info else []
     todo = []
     objs = []
@@ -77,7 +88,7 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None,
             force
             or ptxas_info
             or not os.path.exists(obj)
-            or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time)
+            or os.path.getmtime(obj) < _deps_mtime(src)
         ):
             todo.append((src, obj))
     if todo:

@@ -1,0 +1,265 @@
+"""Functions of the public NumPy-compatible API other than the ufunc objects:
+array creation, views, copies, reductions, ``where`` and helpers.
+
+Keyword handling follows the reference wrappers: ``sum``/``prod``
+(dpnp/dpnp_iface_mathematical.py:4910-5010 with the accumulation type of :96-103),
+``max``/``min``/``mean`` (dpnp/dpnp_iface_statistics.py:1039-1207), ``argmax``/``argmin``
+(dpnp/dpnp_iface_searching.py:69-158), ``where`` (:386-475), the ``out`` handling of
+dpnp/dpnp_utils/dpnp_utils_reduction.py:35-52 and ``get_result_array``
+(dpnp/dpnp_iface.py:495-540): ``initial``/``where`` are not supported, an ``out`` of
+another type receives the result with an unsafe cast.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from . import tensor as dpt
+from .dpnp_array import dpnp_array
+from .tensor import _tensor_impl as ti
+from .tensor._type_utils import DEFAULT_FP, _default_accumulation_dtype
+from .tensor._usmarray import usm_ndarray
+
+
+def _wrap(x):
+    return dpnp_array._create_from_usm_ndarray(x) if isinstance(x, usm_ndarray) else x
+
+
+def is_supported_array_type(a):
+    return isinstance(a, (dpnp_array, usm_ndarray))
+
+
+def get_usm_ndarray(a):
+    """The tensor-level array behind `a` (dpnp/dpnp_iface.py:543-571)."""
+    if isinstance(a, dpnp_array):
+        return a._array_obj
+    if isinstance(a, usm_ndarray):
+        return a
+    raise TypeError(f"An array must be any of supported type, but got {type(a)}")
+
+
+def get_usm_ndarray_or_scalar(a):
+    return a if isinstance(a, (bool, int, float, complex, np.generic)) else get_usm_ndarray(a)
+
+
+def check_limitations(initial=None, where=True, **kw):
+    """Raise NotImplementedError for keywords the device path does not implement."""
+    if initial is not None:
+        raise NotImplementedError(f"initial keyword argument is only supported with its default value, got {initial}")
+    if where is not True:
+        raise NotImplementedError(f"where keyword argument is only supported with its default value, got {where}")
+
+
+def asnumpy(a, order="C"):
+    """Copy to a NumPy array (dpnp/dpnp_iface.py:107-140)."""
+    if isinstance(a, (dpnp_array, usm_ndarray)):
+        return np.asarray(dpt.asnumpy(get_usm_ndarray(a)), order=order)
+    return np.asarray(a, order=order)
+
+
+def default_float_type(device=None, sycl_queue=None):
+    """Default floating type of the device: float64 (dpnp/dpnp_iface.py:309-344)."""
+    return DEFAULT_FP.type
+
+
+def are_same_logical_tensors(a, b):
+    return ti._same_logical_tensors(get_usm_ndarray(a), get_usm_ndarray(b))
+
+
+def copyto(dst, src, casting="same_kind", where=True):
+    if where is not True:
+        raise NotImplementedError("where keyword is not supported")
+    dst_usm = get_usm_ndarray(dst)
+    if isinstance(src, (dpnp_array, usm_ndarray)):
+        src = get_usm_ndarray(src)
+        if not np.can_cast(src.dtype, dst_usm.dtype, casting=casting):
+            raise TypeError(f"Cannot cast from {src.dtype} to {dst_usm.dtype} according to the rule '{casting}'")
+    dst_usm[...] = src
+
+
+def get_result_array(a, out=None, casting="safe"):
+    if out is None:
+        return _wrap(a)
+    out_arr = _wrap(out)
+    a_usm = get_usm_ndarray(a)
+    if a is out or ti._same_logical_tensors(a_usm, out_arr._array_obj):
+        return out_arr
+    if out_arr.shape != a_usm.shape:
+        raise ValueError(f"Output array of shape {a_usm.shape} is needed, got {out_arr.shape}.")
+    copyto(out_arr, a_usm, casting=casting)
+    return out_arr
+
+
+# ---------------------------------------------------------------- creation
+def _creation(fn):
+    def wrapped(*args, like=None, **kwargs):
+        if like is not None:
+            raise NotImplementedError("like keyword is not supported")
+        args = [get_usm_ndarray(a) if isinstance(a, dpnp_array) else a for a in args]
+        return _wrap(fn(*args, **kwargs))
+    wrapped.__name__ = fn.__name__
+    wrapped.__doc__ = fn.__doc__
+    return wrapped
+
+
+empty = _creation(dpt.empty)
+zeros = _creation(dpt.zeros)
+ones = _creation(dpt.ones)
+arange = _creation(dpt.arange)
+empty_like = _creation(dpt.empty_like)
+zeros_like = _creation(dpt.zeros_like)
+ones_like = _creation(dpt.ones_like)
+
+
+def full(shape, fill_value, *, dtype=None, order="C", like=None, device=None, usm_type=None, sycl_queue=None):
+    fv = get_usm_ndarray(fill_value) if isinstance(fill_value, dpnp_array) else fill_value
+    return _wrap(dpt.full(shape, fv, dtype=dtype, order=order, device=device, usm_type=usm_type,
+                          sycl_queue=sycl_queue))
+
+
+def full_like(a, /, fill_value, *, dtype=None, order="K", device=None, usm_type=None, sycl_queue=None):
+    return _wrap(dpt.full_like(get_usm_ndarray(a), fill_value, dtype=dtype, order=order, device=device,
+                               usm_type=usm_type, sycl_queue=sycl_queue))
+
+
+def asarray(a, dtype=None, order=None, *, device=None, usm_type=None, sycl_queue=None, copy=None, like=None):
+    if isinstance(a, dpnp_array):
+        a = a._array_obj
+    return _wrap(dpt.asarray(a, dtype=dtype, order=order or "K", device=device, usm_type=usm_type,
+                             sycl_queue=sycl_queue, copy=copy))
+
+
+def array(a, dtype=None, *, copy=True, order="K", subok=False, ndmin=0, like=None, device=None,
+          usm_type=None, sycl_queue=None):
+    if subok or like is not None:
+        raise NotImplementedError("subok/like keywords are not supported")
+    r = asarray(a, dtype=dtype, order=order, device=device, usm_type=usm_type, sycl_queue=sycl_queue,
+                copy=True if copy else None)
+    if ndmin > r.ndim:
+        r = r.reshape((1,) * (ndmin - r.ndim) + r.shape)
+    return r
+
+
+def astype(x, dtype, /, *, order="K", casting="unsafe", copy=True, device=None):
+    return _wrap(dpt.astype(get_usm_ndarray(x), dtype, order=order, casting=casting, copy=copy))
+
+
+def copy(a, order="K", subok=False):
+    return _wrap(dpt.copy(get_usm_ndarray(a), order=order))
+
+
+# ------------------------------------------------------------------- views
+def transpose(a, axes=None):
+    a = _wrap(a)
+    return a.transpose() if axes is None else a.transpose(*axes)
+
+
+def reshape(a, /, shape=None, order="C", *, newshape=None, copy=None):
+    if shape is None:
+        shape = newshape
+    if shape is None:
+        raise TypeError("reshape() missing 1 required positional argument: 'shape'")
+    if order is None:
+        order = "C"
+    if order in ("A", "a"):
+        u = get_usm_ndarray(a)
+        order = "F" if (u.flags.f_contiguous and not u.flags.c_contiguous) else "C"
+    return _wrap(dpt.reshape(get_usm_ndarray(a), shape, order=order, copy=copy))
+
+
+def broadcast_to(a, /, shape, subok=False):
+    return _wrap(dpt.broadcast_to(get_usm_ndarray(a), shape))
+
+
+def expand_dims(a, axis):
+    return _wrap(dpt.expand_dims(get_usm_ndarray(a), axis))
+
+
+def squeeze(a, /, axis=None):
+    return _wrap(dpt.squeeze(get_usm_ndarray(a), axis))
+
+
+def ravel(a, order="C"):
+    return reshape(a, -1, order=order)
+
+
+# -------------------------------------------------------------- reductions
+def _wrap_reduction_call(usm_a, out, fn, res_dt, **kwargs):
+    input_out = out
+    usm_out = None
+    if out is not None:
+        if not is_supported_array_type(out):
+            raise TypeError(f"An array must be any of supported type, but got {type(out)}")
+        out_usm = get_usm_ndarray(out)
+        # the tensor layer wants the exact result type; other types get the
+        # result through a cast afterwards
+        usm_out = out_usm if out_usm.dtype == res_dt else None
+    kwargs["out"] = usm_out
+    res = fn(usm_a, **kwargs)
+    return get_result_array(res, input_out, casting="unsafe")
+
+
+def _reduction_res_dt(a, dtype):
+    return _default_accumulation_dtype(a.dtype) if dtype is None else np.dtype(dtype)
+
+
+def sum(a, axis=None, dtype=None, out=None, keepdims=False, initial=None, where=True):
+    check_limitations(initial=initial, where=where)
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.sum, _reduction_res_dt(usm_a, dtype), axis=axis,
+                                dtype=dtype, keepdims=keepdims)
+
+
+def prod(a, axis=None, dtype=None, out=None, keepdims=False, initial=None, where=True):
+    check_limitations(initial=initial, where=where)
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.prod, _reduction_res_dt(usm_a, dtype), axis=axis,
+                                dtype=dtype, keepdims=keepdims)
+
+
+def max(a, axis=None, out=None, keepdims=False, initial=None, where=True):
+    check_limitations(initial=initial, where=where)
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.max, usm_a.dtype, axis=axis, keepdims=keepdims)
+
+
+def min(a, axis=None, out=None, keepdims=False, initial=None, where=True):
+    check_limitations(initial=initial, where=where)
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.min, usm_a.dtype, axis=axis, keepdims=keepdims)
+
+
+amax, amin = max, min
+
+
+def argmax(a, axis=None, out=None, *, keepdims=False):
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.argmax, np.dtype("i8"), axis=axis, keepdims=keepdims)
+
+
+def argmin(a, axis=None, out=None, *, keepdims=False):
+    usm_a = get_usm_ndarray(a)
+    return _wrap_reduction_call(usm_a, out, dpt.argmin, np.dtype("i8"), axis=axis, keepdims=keepdims)
+
+
+def mean(a, /, axis=None, dtype=None, out=None, keepdims=False, *, where=True):
+    check_limitations(where=where)
+    res = dpt.mean(get_usm_ndarray(a), axis=axis, keepdims=keepdims)
+    if dtype is not None:
+        res = dpt.astype(res, dtype)
+    return get_result_array(res, out, casting="unsafe")
+
+
+def where(condition, x=None, y=None, /, *, order="K", out=None):
+    """Elements from `x` where `condition` holds, else from `y`
+    (dpnp/dpnp_iface_searching.py:386-475; the one-argument form is not on this path)."""
+    missing = (x is None, y is None).count(True)
+    if missing == 1:
+        raise ValueError("Must provide both 'x' and 'y' or neither.")
+    if missing == 2:
+        raise NotImplementedError("where(condition) alone (nonzero) is not provided by the elementwise path")
+    cond = get_usm_ndarray(condition)
+    xu = get_usm_ndarray_or_scalar(x)
+    yu = get_usm_ndarray_or_scalar(y)
+    res = dpt.where(cond, xu, yu, order=order, out=None if out is None else get_usm_ndarray(out))
+    return get_result_array(res, out)

@@ -1,0 +1,161 @@
+"""NumPy-style ufunc objects of the public API.
+
+``DPNPUnaryFunc`` / ``DPNPBinaryFunc`` add the NumPy keyword handling of the
+reference classes (dpnp/dpnp_algo/dpnp_elementwise_common.py:81-235,537-739) on
+top of the tensor-level function objects: ``out`` (array or 1-tuple), ``where``
+and ``subok`` must keep their defaults, ``dtype`` casts the inputs first and
+excludes ``out``, ``x1 is out`` takes the in-place kernel.  There is no
+vendor-library fast path: every call runs the library's own kernels.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from . import tensor as dpt
+from .dpnp_array import dpnp_array
+from .tensor import _elementwise_funcs as ef
+from .tensor._elementwise_common import BinaryElementwiseFunc, UnaryElementwiseFunc
+from .tensor._usmarray import usm_ndarray
+
+
+def _is_array(x):
+    return isinstance(x, (dpnp_array, usm_ndarray))
+
+
+def _is_scalar(x):
+    return isinstance(x, (bool, int, float, complex, np.generic))
+
+
+def _usm(x):
+    return x._array_obj if isinstance(x, dpnp_array) else x
+
+
+def _check_common_kwargs(name, kwargs, where, subok, dtype, out):
+    if kwargs:
+        raise NotImplementedError(f"Requested function={name} with kwargs={kwargs} isn't currently supported.")
+    if where is not True:
+        raise NotImplementedError(f"Requested function={name} with where={where} isn't currently supported.")
+    if subok is not True:
+        raise NotImplementedError(f"Requested function={name} with subok={subok} isn't currently supported.")
+    if dtype is not None and out is not None:
+        raise TypeError(f"Requested function={name} only takes `out` or `dtype` as an argument, "
+                        "but both were provided.")
+
+
+def _norm_order(order):
+    if order is None:
+        return "K"
+    if isinstance(order, str) and order in "afkcAFKC" and len(order) == 1:
+        return order.upper()
+    raise ValueError(f"order must be one of 'C', 'F', 'A', or 'K' (got '{order}')")
+
+
+def _unpack_out(out, nout=1):
+    if isinstance(out, tuple):
+        if len(out) != nout:
+            raise ValueError("'out' tuple must have exactly one entry per ufunc output")
+        return out[0]
+    return out
+
+
+class DPNPUnaryFunc(UnaryElementwiseFunc):
+    def __init__(self, base: UnaryElementwiseFunc, name=None, docs=None):
+        super().__init__(name or base.name_, base.result_type_resolver_fn_, base.unary_fn_,
+                         docs or base.__doc__, acceptance_fn=base.acceptance_fn_)
+        self.__name__ = "DPNPUnaryFunc"
+
+    def __call__(self, x, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
+        _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+        if not _is_array(x):
+            raise TypeError(f"Input array must be any of supported type, but got {type(x)}")
+        order = _norm_order(order)
+        x_usm = _usm(x)
+        if dtype is not None:
+            x_usm = dpt.astype(x_usm, dtype, copy=False)
+        out = _unpack_out(out)
+        if out is not None and not _is_array(out):
+            raise TypeError(f"output array must be any of supported type, but got {type(out)}")
+        res = super().__call__(x_usm, out=None if out is None else _usm(out), order=order)
+        if out is not None and isinstance(out, dpnp_array):
+            return out
+        return dpnp_array._create_from_usm_ndarray(res)
+
+
+class DPNPBinaryFunc(BinaryElementwiseFunc):
+    def __init__(self, base: BinaryElementwiseFunc, name=None, docs=None):
+        super().__init__(name or base.name_, base.result_type_resolver_fn_, base.binary_fn_,
+                         docs or base.__doc__, binary_inplace_fn=base.binary_inplace_fn_,
+                         acceptance_fn=base.acceptance_fn_, weak_type_resolver=base.weak_type_resolver_)
+        self.__name__ = "DPNPBinaryFunc"
+
+    def __call__(self, x1, x2, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
+        for x in (x1, x2):
+            if not (_is_array(x) or _is_scalar(x)):
+                raise TypeError(f"An array must be any of supported type, but got {type(x)}")
+        if not (_is_array(x1) or _is_array(x2)):
+            raise TypeError("Input should be any of supported array type, got two scalars")
+        _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+        x1_usm, x2_usm = _usm(x1), _usm(x2)
+        out = _unpack_out(out)
+        if out is not None and not _is_array(out):
+            raise TypeError(f"output array must be any of supported type, but got {type(out)}")
+        out_usm = None if out is None else _usm(out)
+        if isinstance(x1, dpnp_array) and x1 is out and order == "K" and dtype is None:
+            super()._inplace_op(x1_usm, x2_usm)
+            return x1
+        order = _norm_order(order)
+        if dtype is not None:
+            if _is_scalar(x1):
+                x1_usm = dpt.asarray(x1, dtype=dtype, sycl_queue=x2_usm.sycl_queue)
+                x2_usm = dpt.astype(x2_usm, dtype, copy=False)
+            elif _is_scalar(x2):
+                x1_usm = dpt.astype(x1_usm, dtype, copy=False)
+                x2_usm = dpt.asarray(x2, dtype=dtype, sycl_queue=x1_usm.sycl_queue)
+            else:
+                x1_usm = dpt.astype(x1_usm, dtype, copy=False)
+                x2_usm = dpt.astype(x2_usm, dtype, copy=False)
+        res = super().__call__(x1_usm, x2_usm, out=out_usm, order=order)
+        if out is not None and isinstance(out, dpnp_array):
+            return out
+        return dpnp_array._create_from_usm_ndarray(res)
+
+
+# unary
+abs = absolute = DPNPUnaryFunc(ef.abs, "abs")
+negative = DPNPUnaryFunc(ef.negative)
+positive = DPNPUnaryFunc(ef.positive)
+exp = DPNPUnaryFunc(ef.exp)
+log = DPNPUnaryFunc(ef.log)
+sqrt = DPNPUnaryFunc(ef.sqrt)
+erf = DPNPUnaryFunc(ef.erf)
+square = DPNPUnaryFunc(ef.square)
+reciprocal = DPNPUnaryFunc(ef.reciprocal)
+sin = DPNPUnaryFunc(ef.sin)
+cos = DPNPUnaryFunc(ef.cos)
+tanh = DPNPUnaryFunc(ef.tanh)
+expm1 = DPNPUnaryFunc(ef.expm1)
+log1p = DPNPUnaryFunc(ef.log1p)
+floor = DPNPUnaryFunc(ef.floor)
+ceil = DPNPUnaryFunc(ef.ceil)
+sign = DPNPUnaryFunc(ef.sign)
+logical_not = DPNPUnaryFunc(ef.logical_not)
+isnan = DPNPUnaryFunc(ef.isnan)
+isfinite = DPNPUnaryFunc(ef.isfinite)
+isinf = DPNPUnaryFunc(ef.isinf)
+# binary
+add = DPNPBinaryFunc(ef.add)
+subtract = DPNPBinaryFunc(ef.subtract)
+multiply = DPNPBinaryFunc(ef.multiply)
+divide = true_divide = DPNPBinaryFunc(ef.divide, "divide")
+maximum = DPNPBinaryFunc(ef.maximum)
+minimum = DPNPBinaryFunc(ef.minimum)
+power = DPNPBinaryFunc(ef.pow, "power")
+equal = DPNPBinaryFunc(ef.equal)
+not_equal = DPNPBinaryFunc(ef.not_equal)
+less = DPNPBinaryFunc(ef.less)
+less_equal = DPNPBinaryFunc(ef.less_equal)
+greater = DPNPBinaryFunc(ef.greater)
+greater_equal = DPNPBinaryFunc(ef.greater_equal)
+logical_and = DPNPBinaryFunc(ef.logical_and)
+logical_or = DPNPBinaryFunc(ef.logical_or)

@@ -57,6 +57,7 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct SumRed {
         else return Acc(0);
     }
     static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
     static DPB_D Acc combine(Acc a, Acc b)
     {
         if constexpr (is_bool_v<Acc>) return bool_t(a.v || b.v);
@@ -78,6 +79,7 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ProdRed {
         else return Acc(1);
     }
     static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
     static DPB_D Acc combine(Acc a, Acc b)
     {
         if constexpr (is_bool_v<Acc>) return bool_t(a.v && b.v);
@@ -96,6 +98,7 @@ template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struc
     using Stage2 = ExtremeRed<IS_MAX, Acc, TOut, Acc>;
     static DPB_D Acc identity() { return IS_MAX ? lowest_value<Acc>() : highest_value<Acc>(); }
     static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
     static DPB_D Acc combine(Acc a, Acc b)
     {
         if constexpr (is_bool_v<Acc>) return IS_MAX ? bool_t(a.v || b.v) : bool_t(a.v && b.v);
@@ -159,6 +162,29 @@ struct SearchRed {
             else a.val = convert<V>(v);
             a.idx = i;
             return a;
+        }
+    }
+    // Accumulate one element whose index is larger than every index this
+    // accumulator has seen: it wins only if strictly better (or if nothing
+    // has been seen yet).
+    static DPB_D Acc step(const Acc &a, const In &v, int64_t i)
+    {
+        if constexpr (STAGE2) {
+            return combine(a, v);
+        }
+        else {
+            V x;
+            if constexpr (is_bool_v<TIn>) x = v.v ? 1 : 0;
+            else x = convert<V>(v);
+            bool wins = IS_MAX ? (x > a.val) : (x < a.val);
+            if constexpr (std::is_floating_point_v<V>) wins = wins || (x != x && !(a.val != a.val));
+            wins = wins || (a.idx == std::numeric_limits<int64_t>::max());
+            Acc r = a;
+            if (wins) {
+                r.val = x;
+                r.idx = i;
+            }
+            return r;
         }
     }
     static DPB_D Acc combine(const Acc &a, const Acc &b) { return search_better<IS_MAX>(a, b) ? a : b; }

@@ -1,0 +1,210 @@
+"""Execution queues and device memory.
+
+``StreamQueue`` stands where the reference carries a ``dpctl.SyclQueue``: it
+names a CUDA device and one in-order ``cudaStream_t`` on it.  Work submitted to
+one queue runs in submission order, which is the guarantee the reference
+obtains from ``SequentialOrderManager`` (dpnp/tensor/_elementwise_common.py:240-254).
+
+``MemoryUSMDevice`` owns one block of the stream-ordered pool and replaces
+``dpctl.memory.MemoryUSMDevice`` as wrapped by dpnp/memory/_memory.py:36-110.
+Freeing is ordered after the work already queued on the owning stream, so a
+block may be released while kernels that use it are still in flight.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+from . import _lib
+from ._lib import check, lib
+
+__all__ = [
+    "StreamQueue", "get_default_queue", "MemoryUSMDevice", "MemoryUSMShared", "MemoryUSMHost",
+    "create_data", "pool_stats", "pool_trim", "pool_set_limit", "ExecutionPlacementError",
+]
+
+
+class ExecutionPlacementError(Exception):
+    """Arrays of one operation live on different devices/queues
+    (mirrors dpctl.utils.ExecutionPlacementError)."""
+
+
+class StreamQueue:
+    """A CUDA device ordinal plus one in-order stream on that device."""
+
+    __slots__ = ("device", "_stream", "__weakref__")
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.device = int(device)
+        if stream is None:
+            check(lib.dpb_set_device(self.device))
+            h = C.c_void_p()
+            check(lib.dpb_stream_create(C.byref(h)))
+            self._stream = h.value or 0
+        else:
+            self._stream = int(stream)
+
+    @property
+    def stream(self) -> int:
+        """The cudaStream_t as an integer."""
+        return self._stream
+
+    # names used by code written against dpctl
+    @property
+    def sycl_device(self):
+        return self.device
+
+    def activate(self) -> None:
+        check(lib.dpb_set_device(self.device))
+
+    def wait(self) -> None:
+        self.activate()
+        check(lib.dpb_stream_synchronize(C.c_void_p(self._stream)))
+
+    synchronize = wait
+
+    def __eq__(self, other):
+        return (
+            isinstance(other, StreamQueue)
+            and other.device == self.device
+            and other._stream == self._stream
+        )
+
+    def __hash__(self):
+        return hash((self.device, self._stream))
+
+    def __repr__(self):
+        return f"<StreamQueue cuda:{self.device} stream=0x{self._stream:x}>"
+
+
+_default_queues: dict[int, StreamQueue] = {}
+_default_lock = threading.Lock()
+_current_device = [None]
+
+
+def _require_device() -> None:
+    if _lib.device_count() == 0:
+        raise RuntimeError(
+            "dpnp_b200 needs a CUDA device: none is visible and there is no CPU fallback"
+        )
+
+
+def get_default_queue(device: int | None = None) -> StreamQueue:
+    """The library-wide queue of `device` (default: the selected device)."""
+    if device is None:
+        device = _current_device[0] if _current_device[0] is not None else 0
+    q = _default_queues.get(device)
+    if q is None:
+        with _default_lock:
+            q = _default_queues.get(device)
+            if q is None:
+                _require_device()
+                q = StreamQueue(device)
+                _default_queues[device] = q
+    return q
+
+
+def select_default_device(device: int) -> None:
+    """Choose the device new arrays are allocated on when none is given."""
+    _current_device[0] = int(device)
+
+
+def normalize_queue(sycl_queue=None, device=None) -> StreamQueue:
+    """Queue from the `sycl_queue=` / `device=` keywords accepted by creation functions."""
+    if sycl_queue is not None:
+        if not isinstance(sycl_queue, StreamQueue):
+            raise TypeError(f"expected a StreamQueue, got {type(sycl_queue)}")
+        return sycl_queue
+    if device is None:
+        return get_default_queue()
+    if isinstance(device, StreamQueue):
+        return device
+    if isinstance(device, str):
+        # accept "cuda", "cuda:1", "gpu", "gpu:1"
+        name, _, idx = device.partition(":")
+        if name not in ("cuda", "gpu"):
+            raise ValueError(f"unknown device string {device!r}")
+        return get_default_queue(int(idx) if idx else 0)
+    return get_default_queue(int(device))
+
+
+class MemoryUSMDevice:
+    """A block of device memory from the stream-ordered pool."""
+
+    usm_type = "device"
+
+    def __init__(self, nbytes: int, queue: StreamQueue | None = None):
+        nbytes = int(nbytes)
+        if nbytes < 0:
+            raise ValueError("nbytes must be non-negative")
+        self.sycl_queue = queue if queue is not None else get_default_queue()
+        self.nbytes = nbytes
+        self._ptr = 0
+        self.sycl_queue.activate()
+        p = C.c_void_p()
+        check(lib.dpb_malloc(nbytes, C.c_void_p(self.sycl_queue.stream), C.byref(p)))
+        self._ptr = p.value or 0
+
+    @property
+    def ptr(self) -> int:
+        """Device address of the first byte (dpnp/memory/_memory.py:36-67 adds the same)."""
+        return self._ptr
+
+    @property
+    def size(self) -> int:
+        return self.nbytes
+
+    def __len__(self):
+        return self.nbytes
+
+    def free(self) -> None:
+        ptr, self._ptr = self._ptr, 0
+        if ptr:
+            try:
+                lib.dpb_set_device(self.sycl_queue.device)
+                lib.dpb_free(C.c_void_p(ptr), C.c_void_p(self.sycl_queue.stream))
+            except Exception:  # interpreter shutdown
+                pass
+
+    def __del__(self):
+        self.free()
+
+    def __repr__(self):
+        return f"<{type(self).__name__} {self.nbytes} bytes at 0x{self._ptr:x} on cuda:{self.sycl_queue.device}>"
+
+
+class MemoryUSMShared(MemoryUSMDevice):
+    """Accepted for API compatibility; backed by device memory."""
+
+    usm_type = "shared"
+
+
+class MemoryUSMHost(MemoryUSMDevice):
+    """Accepted for API compatibility; backed by device memory."""
+
+    usm_type = "host"
+
+
+def create_data(x):
+    """Return the memory object behind an array (dpnp/memory/_memory.py:70-110)."""
+    base = getattr(x, "usm_data", None)
+    if base is None:
+        raise TypeError(f"expected an array with device memory, got {type(x)}")
+    return base
+
+
+def pool_stats() -> dict:
+    """Counters of the current device's pool."""
+    vals = [C.c_size_t() for _ in range(4)]
+    check(lib.dpb_pool_stats(*[C.byref(v) for v in vals]))
+    keys = ("reserved", "used", "reserved_high", "used_high")
+    return {k: v.value for k, v in zip(keys, vals)}
+
+
+def pool_trim(keep_bytes: int = 0) -> None:
+    check(lib.dpb_pool_trim(int(keep_bytes)))
+
+
+def pool_set_limit(max_live_bytes: int) -> None:
+    check(lib.dpb_pool_set_limit(int(max_live_bytes)))
