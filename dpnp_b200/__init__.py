@@ -12,9 +12,9 @@ argmax, argmin.  All compute runs in hand-written CUDA kernels of
 import numpy as _np
 
 from . import _lib, memory, random, scipy, tensor
-from ._iface import (amax, amin, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
+from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
                      asnumpy, astype, broadcast_to, check_limitations, copy, copyto,
-                     default_float_type, empty, empty_like, expand_dims, full, full_like,
+                     default_float_type, empty, empty_like, expand_dims, flip, full, full_like,
                      get_result_array, get_usm_ndarray, get_usm_ndarray_or_scalar,
                      is_supported_array_type, max, mean, min, ones, ones_like, prod, ravel, reshape,
                      squeeze, sum, transpose, where, zeros, zeros_like)

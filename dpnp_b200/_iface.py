@@ -263,3 +263,17 @@ def where(condition, x=None, y=None, /, *, order="K", out=None):
     yu = get_usm_ndarray_or_scalar(y)
     res = dpt.where(cond, xu, yu, order=order, out=None if out is None else get_usm_ndarray(out))
     return get_result_array(res, out)
+
+
+def flip(m, axis=None):
+    return _wrap(dpt.flip(get_usm_ndarray(m), axis=axis))
+
+
+def all(a, /, axis=None, out=None, keepdims=False, *, where=True):
+    check_limitations(where=where)
+    return get_result_array(dpt.all(get_usm_ndarray(a), axis=axis, keepdims=keepdims), out)
+
+
+def any(a, /, axis=None, out=None, keepdims=False, *, where=True):
+    check_limitations(where=where)
+    return get_result_array(dpt.any(get_usm_ndarray(a), axis=axis, keepdims=keepdims), out)

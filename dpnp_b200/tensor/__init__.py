@@ -14,8 +14,8 @@ from ._elementwise_funcs import (abs, add, ceil, cos, divide, equal, erf, exp, e
                                  negative, not_equal, positive, pow, reciprocal, sign, sin, sqrt,
                                  square, subtract, tanh)
 from ._manipulation_functions import (broadcast_arrays, broadcast_shapes, broadcast_to, expand_dims,
-                                      permute_dims, reshape, squeeze)
-from ._reduction import argmax, argmin, max, min, prod, sum
+                                      flip, permute_dims, reshape, squeeze)
+from ._reduction import all, any, argmax, argmin, max, min, prod, sum
 from ._search_functions import where
 from ._statistical_functions import mean
 from ._type_utils import can_cast, result_type

@@ -199,3 +199,12 @@ def reshape(x, shape, /, *, order="C", copy=None):
     c = _copy(x, order="C")
     from ._usmarray import _dense_strides
     return c._like(c._ptr, shape, _dense_strides(shape))
+
+
+def flip(x, /, *, axis=None):
+    """Reverse the order of elements along the given axes (a view with negated strides)."""
+    if not isinstance(x, usm_ndarray):
+        raise TypeError(f"Expected usm_ndarray type, got {type(x)}.")
+    axes = tuple(range(x.ndim)) if axis is None else normalize_axis_tuple(axis, x.ndim)
+    key = tuple(slice(None, None, -1) if i in axes else slice(None) for i in range(x.ndim))
+    return x[key]

@@ -207,3 +207,42 @@ def argmax(x, /, *, axis=None, keepdims=False, out=None):
 def argmin(x, /, *, axis=None, keepdims=False, out=None):
     """Index of the first minimum along an axis (flattened when axis is None)."""
     return _search_over_axis(x, axis, keepdims, out, tri._argmin_over_axis)
+
+
+def _boolean_reduction(x, axis, keepdims, fn):
+    """all/any: the array is first reduced to its truth values, then max/min of
+    booleans is logical or/and (the reference has dedicated kernels,
+    source/reductions/reduction_over_axis.hpp:1053-1303; the results are the same)."""
+    if not isinstance(x, usm_ndarray):
+        raise TypeError(f"Expected dpnp.tensor.usm_ndarray, got {type(x)}")
+    from ._copy_utils import astype
+    b = x if x.dtype == np.bool_ else astype(x, np.bool_)
+    if b.size == 0 or any_zero_axis(b, axis):
+        # empty reductions: all -> True, any -> False
+        from ._ctors import full
+        nd = b.ndim
+        axes = tuple(range(nd)) if axis is None else normalize_axis_tuple(
+            axis if isinstance(axis, (tuple, list)) else (axis,), nd)
+        shape = tuple((1 if i in axes else s) for i, s in enumerate(b.shape) if keepdims or i not in axes)
+        return full(shape, fn is min, dtype=np.bool_, sycl_queue=x.sycl_queue)
+    return fn(b, axis=axis, keepdims=keepdims)
+
+
+def any_zero_axis(x, axis):
+    nd = x.ndim
+    axes = range(nd) if axis is None else normalize_axis_tuple(
+        axis if isinstance(axis, (tuple, list)) else (axis,), nd)
+    for i in axes:
+        if x.shape[i] == 0:
+            return True
+    return False
+
+
+def all(x, /, *, axis=None, keepdims=False):
+    """True where every element along the axes is non-zero."""
+    return _boolean_reduction(x, axis, keepdims, min)
+
+
+def any(x, /, *, axis=None, keepdims=False):
+    """True where some element along the axes is non-zero."""
+    return _boolean_reduction(x, axis, keepdims, max)

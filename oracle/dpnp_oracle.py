@@ -1,0 +1,232 @@
+"""TEST INFRASTRUCTURE, not product code: the CPU oracle for the elementwise and
+reduction path of dpnp.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the ``cpu_baseline`` /
+``--impl reference`` legs of ``bench.py`` may import this module.  It restates,
+with NumPy on the host, what the reference computes for the path, citing the
+reference code each function follows (paths relative to the root of
+IntelPython/dpnp), and loads two native helpers:
+
+* ``liboracle_core.so`` -- the plain-C restatement in ``oracle_core.c``;
+* ``_ref/libref_strided_iters.so`` -- the reference's own iteration-space
+  simplifier compiled from its SYCL-free header (``kind: reference`` evidence
+  for that one piece of host logic).
+
+Parity status: the reference itself cannot be built or imported in this
+environment (DPC++/SYCL, dpctl and oneMKL are absent), so the oracle is pinned
+against the known-answer cases of the reference's tests (``tests/golden``) and
+against NumPy/SciPy, which those tests use as their own oracle.  For
+exp/log/erf the reference's arithmetic lives in oneMKL VM / the SYCL device
+library: at the 2-ulp level PARITY IS UNPINNED; the tests bound the CUDA
+results against correctly rounded values (mpmath) instead.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+CORE_PATH = os.path.join(_HERE, "liboracle_core.so")
+REF_PATH = os.path.join(_HERE, "_ref", "libref_strided_iters.so")
+
+_core = None
+_ref = None
+
+
+def core():
+    """The C restatement (built by ``make -C oracle`` / ``__graft_entry__.build()``)."""
+    global _core
+    if _core is None:
+        if not os.path.exists(CORE_PATH):
+            raise RuntimeError(f"{CORE_PATH} is missing: run `make -C oracle`")
+        _core = C.CDLL(CORE_PATH)
+    return _core
+
+
+def ref_strided_iters():
+    """The reference's simplifier, or None when it was not built."""
+    global _ref
+    if _ref is None and os.path.exists(REF_PATH):
+        _ref = C.CDLL(REF_PATH)
+    return _ref
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+# --------------------------------------------------------------- promotion
+def binary_result(op, x1, x2):
+    """Elementwise binary op with the reference's promotion rules: NumPy's
+    result for same-kind safe promotion (dpnp/tensor/_type_utils.py:218-251), true
+    division of integers in the default floating type (:89-107), Python scalars
+    weak (NEP 50, :389-426).  The reference's tests take NumPy as the expected
+    value (dpnp/tests/tensor/elementwise/test_add.py:49-88)."""
+    fn = {"add": np.add, "subtract": np.subtract, "multiply": np.multiply, "divide": np.true_divide,
+          "maximum": np.maximum, "minimum": np.minimum, "less": np.less, "less_equal": np.less_equal,
+          "greater": np.greater, "greater_equal": np.greater_equal, "equal": np.equal,
+          "not_equal": np.not_equal, "logical_and": np.logical_and, "logical_or": np.logical_or,
+          "power": np.power}[op]
+    with np.errstate(all="ignore"):
+        return fn(x1, x2)
+
+
+def unary_result(op, x):
+    """Elementwise unary op (include/kernels/elementwise_functions/<op>.hpp).  erf
+    follows dpnp/backend/kernels/elementwise_functions/erf.hpp:51-99 (float16 -> float32)."""
+    if op == "erf":
+        import scipy.special as sp
+
+        if x.dtype == np.float16:
+            return sp.erf(x.astype(np.float32))
+        return sp.erf(x)
+    fn = {"exp": np.exp, "log": np.log, "sqrt": np.sqrt, "negative": np.negative, "abs": np.abs,
+          "square": np.square, "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "expm1": np.expm1,
+          "log1p": np.log1p, "floor": np.floor, "ceil": np.ceil, "sign": np.sign,
+          "reciprocal": np.reciprocal, "positive": np.positive, "logical_not": np.logical_not,
+          "isnan": np.isnan, "isinf": np.isinf, "isfinite": np.isfinite}[op]
+    with np.errstate(all="ignore"):
+        return fn(x)
+
+
+def where(cond, x1, x2):
+    """dst = cond ? x1 : x2, any non-zero condition is true (include/kernels/where.hpp:108-110)."""
+    return np.where(np.asarray(cond) != 0, x1, x2)
+
+
+# -------------------------------------------------------------- reductions
+def default_accumulation_dtype(dt):
+    """dpnp/tensor/_type_utils.py:932-952."""
+    dt = np.dtype(dt)
+    if dt.kind in "bi":
+        return np.dtype("i8")
+    if dt.kind == "u":
+        return np.dtype("u8")
+    return dt
+
+
+def sum_exact(x, axis=None):
+    """(sum, sum of magnitudes) in extended precision: the float128/Kahan oracle.
+    np.longdouble is the 80-bit x87 type here (64-bit mantissa)."""
+    xl = np.asarray(x, dtype=np.longdouble)
+    return np.sum(xl, axis=axis), np.sum(np.abs(xl), axis=axis)
+
+
+def sum_int(x, axis=None, dtype=None):
+    """Integer/bool sums are exact modulo 2^bits in the accumulation type
+    (source/reductions/sum.cpp:87-241); bool -> bool is logical or (:268-270)."""
+    x = np.asarray(x)
+    dt = default_accumulation_dtype(x.dtype) if dtype is None else np.dtype(dtype)
+    if dt == np.bool_:
+        return np.any(x != 0, axis=axis)
+    return np.sum(x, axis=axis, dtype=dt)
+
+
+def max_(x, axis=None):
+    """NaN-propagating maximum (include/utils/sycl_utils.hpp:332-352) == np.max."""
+    return np.max(x, axis=axis)
+
+
+def min_(x, axis=None):
+    return np.min(x, axis=axis)
+
+
+def argmax(x, axis=None):
+    """First occurrence of the maximum, NaN is the maximum
+    (include/kernels/reductions.hpp:1933-1963,2062-2117) == np.argmax."""
+    return np.argmax(x, axis=axis)
+
+
+def argmin(x, axis=None):
+    return np.argmin(x, axis=axis)
+
+
+def mean(x, axis=None):
+    """sum in the result type, then one division (dpnp/tensor/_statistical_functions.py:216-269).
+    Computed here in extended precision; compare with a tolerance."""
+    x = np.asarray(x)
+    res_dt = x.dtype if x.dtype.kind in "fc" else np.dtype("f8")
+    return np.mean(np.asarray(x, dtype=np.longdouble), axis=axis).astype(res_dt)
+
+
+# ------------------------------------------------------------ Black-Scholes
+def black_scholes_chain(price, strike, t, rate, vol, xp=np, erf=None):
+    """The expression chain of examples/example_bs.py:50-75 with array module `xp`."""
+    if erf is None:
+        import scipy.special as sp
+
+        erf = sp.erf
+    mr = -rate
+    sig_sig_two = vol * vol * 2
+    a = xp.log(price / strike)
+    b = t * mr
+    z = t * sig_sig_two
+    c = 0.25 * z
+    y = 1.0 / xp.sqrt(z)
+    w1 = (a - b + c) * y
+    w2 = (a - b - c) * y
+    d1 = 0.5 + 0.5 * erf(w1)
+    d2 = 0.5 + 0.5 * erf(w2)
+    se = xp.exp(b) * strike
+    r = price * d1 - se * d2
+    return r, r - price + se
+
+
+def black_scholes_c(price, strike, t, rate, vol, threads=False):
+    """Same chain through the C restatement (libm), optionally on all cores."""
+    n = price.size
+    call = np.empty(n)
+    put = np.empty(n)
+    fn = core().orc_black_scholes_f64_mt if threads else core().orc_black_scholes_f64
+    fn(C.c_int64(n), _p(price), _p(strike), _p(t), C.c_double(rate), C.c_double(vol), _p(call), _p(put))
+    return call, put
+
+
+# ------------------------------------------------------- iteration spaces
+def simplify_ref(shape, strides_list):
+    """Collapse with the reference's own code; returns (shape, strides_list, offsets)."""
+    lib = ref_strided_iters()
+    if lib is None:
+        raise RuntimeError("oracle/_ref is not built")
+    nd, k = len(shape), len(strides_list)
+    sh = (C.c_int64 * max(nd, 1))(*shape)
+    st = (C.c_int64 * max(nd * k, 1))(*[s for row in strides_list for s in row])
+    off = (C.c_int64 * 4)()
+    m = lib.ref_simplify(k, nd, sh, st, off)
+    return list(sh[:m]), [list(st[a * nd:a * nd + m]) for a in range(k)], list(off[:k])
+
+
+def displacement_set(shape, strides_list, offsets=None):
+    """Set of displacement tuples visited by an iteration space (brute force)."""
+    import itertools
+
+    offsets = offsets or [0] * len(strides_list)
+    out = set()
+    for idx in itertools.product(*[range(s) for s in shape]):
+        out.add(tuple(o + sum(i * s for i, s in zip(idx, st)) for st, o in zip(strides_list, offsets)))
+    return out
+
+
+# --------------------------------------------------------------------- ulp
+def ulp_distance(got, exact_longdouble):
+    """|got - exact| in units of the last place of `got`'s type at `exact`."""
+    got = np.asarray(got)
+    ex = np.asarray(exact_longdouble, dtype=np.longdouble)
+    spacing = np.spacing(np.abs(ex).astype(got.dtype)).astype(np.longdouble)
+    return np.abs(got.astype(np.longdouble) - ex) / spacing
+
+
+def mp_reference(fn_name, x, digits=40):
+    """Correctly rounded reference values of exp/log/erf at the points x, as longdouble."""
+    import mpmath
+
+    mpmath.mp.dps = digits
+    f = {"exp": mpmath.exp, "log": mpmath.log, "erf": mpmath.erf, "sqrt": mpmath.sqrt}[fn_name]
+    out = np.empty(len(x), dtype=np.longdouble)
+    for i, v in enumerate(np.asarray(x, dtype=np.float64)):
+        out[i] = np.longdouble(mpmath.nstr(f(mpmath.mpf(float(v))), 25))
+    return out
