@@ -1,0 +1,565 @@
+#!/usr/bin/env python
+"""Measurement harness for the elementwise/reduction path.
+
+    python bench.py --gpus N --steps K --warmup W            # the CUDA path (this library)
+    python bench.py --impl reference --steps K --warmup W    # the CPU arm
+
+Workload of the headline number (``config.workload``): Black-Scholes call/put
+pricing of 2^26 options in float64, written exactly as examples/example_bs.py of
+the reference writes it -- 26 elementwise ufunc calls and 2 copies through the
+dpnp-style API.  One step = one evaluation of the chain on one batch.  The
+metric is achieved HBM GB/s counted in ALGORITHMIC bytes: 552 bytes per option
+(24 B per array-array op, 16 B per unary / array-scalar op or copy).  Inputs are
+synthetic (seeded uniform draws with the example's ranges).
+
+`value`  : inputs resident in HBM, CUDA-event time of K steps, max over ranks.
+`e2e`    : same chain, every step copies its three input vectors from pinned
+           host memory and reads call/put back to pinned host memory.
+`roofline`: the contiguous elementwise kernel (ew_contig_vec), algorithmic bytes
+           of the 26 ufunc launches / their summed CUDA-event durations.
+`cpu_baseline`: the C restatement of the chain (oracle/, OpenMP over all host
+           cores) on a bounded sample; same 552 B/option accounting.
+`ops`    : the other benchmark configurations (add f32 2^24; fused Black-Scholes;
+           sum axis=1 / axis=0 / mean of f32 16384x65536; transposed broadcast
+           multiply; max/argmax of int32 (8, 2^29)), each timed on its own.
+
+With N > 1 (torchrun, one rank per GPU) every rank prices its own 2^26 options
+(weak scaling, no data-path collective); the reduction configurations are
+sharded on the leading axis and combined with NCCL.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_OPTIONS = 1 << 26
+BYTES_PER_OPTION_CHAIN = 552      # 26 ufunc calls + 2 copies, algorithmic
+BYTES_PER_OPTION_UFUNCS = 520     # the 26 ufunc launches alone
+BYTES_PER_OPTION_FUSED = 40       # 3 loads + 2 stores
+RATE, VOL = 0.1, 0.2
+SEED = 7777777
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.device)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=6)
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------- CUDA helpers
+class Events:
+    def __init__(self, lib, check, stream):
+        self.lib, self.check, self.stream = lib, check, C.c_void_p(stream)
+
+    def new(self):
+        e = C.c_void_p()
+        self.check(self.lib.dpb_event_create(C.byref(e)))
+        return e
+
+    def record(self, e):
+        self.check(self.lib.dpb_event_record(e, self.stream))
+
+    def elapsed_ms(self, e0, e1):
+        self.check(self.lib.dpb_event_synchronize(e1))
+        ms = C.c_float()
+        self.check(self.lib.dpb_event_elapsed_ms(e0, e1, C.byref(ms)))
+        return float(ms.value)
+
+
+def black_scholes(np_, price, strike, t, rate, vol, call, put, hook=None):
+    """The body of examples/example_bs.py::black_scholes; `hook` wraps every array operation
+    (used to time the individual launches)."""
+    h = hook or (lambda nbytes, f: f())
+    n8 = 8
+    mr = -rate
+    sig_sig_two = vol * vol * 2
+    P, S, T = price, strike, t
+    q = h(3 * n8, lambda: P / S)
+    a = h(2 * n8, lambda: np_.log(q))
+    b = h(2 * n8, lambda: T * mr)
+    z = h(2 * n8, lambda: T * sig_sig_two)
+    c = h(2 * n8, lambda: 0.25 * z)
+    sq = h(2 * n8, lambda: np_.sqrt(z))
+    y = h(2 * n8, lambda: 1.0 / sq)
+    ab1 = h(3 * n8, lambda: a - b)
+    abc1 = h(3 * n8, lambda: ab1 + c)
+    w1 = h(3 * n8, lambda: abc1 * y)
+    ab2 = h(3 * n8, lambda: a - b)
+    abc2 = h(3 * n8, lambda: ab2 - c)
+    w2 = h(3 * n8, lambda: abc2 * y)
+    e1 = h(2 * n8, lambda: np_.erf(w1))
+    he1 = h(2 * n8, lambda: 0.5 * e1)
+    d1 = h(2 * n8, lambda: 0.5 + he1)
+    e2 = h(2 * n8, lambda: np_.erf(w2))
+    he2 = h(2 * n8, lambda: 0.5 * e2)
+    d2 = h(2 * n8, lambda: 0.5 + he2)
+    eb = h(2 * n8, lambda: np_.exp(b))
+    Se = h(3 * n8, lambda: eb * S)
+    pd1 = h(3 * n8, lambda: P * d1)
+    sd2 = h(3 * n8, lambda: Se * d2)
+    r = h(3 * n8, lambda: pd1 - sd2)
+    call[:] = r
+    rp = h(3 * n8, lambda: r - P)
+    pt = h(3 * n8, lambda: rp + Se)
+    put[:] = pt
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_chain_throughput(n_sample, min_seconds=8.0, max_reps=6):
+    """Options/s of the C restatement of the chain on all host cores (bounded sample)."""
+    from oracle import dpnp_oracle as orc
+
+    rng = np.random.default_rng(SEED)
+    p, k, t = rng.uniform(10, 50, n_sample), rng.uniform(10, 50, n_sample), rng.uniform(1, 2, n_sample)
+    orc.black_scholes_c(p[:1024], k[:1024], t[:1024], RATE, VOL, threads=True)  # warm up the thread pool
+    reps, total = 0, 0.0
+    best = float("inf")
+    while reps < max_reps and (total < min_seconds or reps < 2):
+        t0 = time.perf_counter()
+        orc.black_scholes_c(p, k, t, RATE, VOL, threads=True)
+        dt = time.perf_counter() - t0
+        best = min(best, dt)
+        total += dt
+        reps += 1
+    return n_sample / best, reps, total
+
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+    """The CPU arm: the reference cannot be installed here (needs DPC++/SYCL, dpctl, oneMKL), so the
+    oracle's C restatement of the same chain is timed on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_sample = 1 << 24
+    # warm-up steps
+    from oracle import dpnp_oracle as orc
+
+    rng = np.random.default_rng(SEED)
+    p, k, t = rng.uniform(10, 50, n_sample), rng.uniform(10, 50, n_sample), rng.uniform(1, 2, n_sample)
+    for _ in range(max(args.warmup, 1)):
+        orc.black_scholes_c(p, k, t, RATE, VOL, threads=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.black_scholes_c(p, k, t, RATE, VOL, threads=True)
+    dt = time.perf_counter() - t0
+    opt_per_s = n_sample * args.steps / dt
+    value = opt_per_s * BYTES_PER_OPTION_CHAIN / 1e9
+    sample = f"2^24 of the 2^26 options per step, {args.steps} steps, C chain with libm on {cpu_threads()} threads"
+    line = {
+        "impl": "reference", "metric": "achieved algorithmic GB/s, Black-Scholes chain (552 B/option)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3 * (N_OPTIONS / n_sample), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "black_scholes_f64_2^26_chain_26ufuncs_2copies", "options": N_OPTIONS,
+                   "rate": RATE, "vol": VOL, "seed": SEED},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference not installable offline (DPC++/SYCL, dpctl, oneMKL absent): CPU port timed instead",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+def timed_steps(ev, fn, steps, flush=None):
+    """CUDA-event time (ms) of `steps` back-to-back calls of fn."""
+    e0, e1 = ev.new(), ev.new()
+    ev.record(e0)
+    for _ in range(steps):
+        fn()
+    ev.record(e1)
+    return ev.elapsed_ms(e0, e1)
+
+
+def median_time_ms(ev, fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = ev.new(), ev.new()
+        ev.record(e0)
+        fn()
+        ev.record(e1)
+        ts.append(ev.elapsed_ms(e0, e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def run_gpu_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib, memory, sharded
+    from dpnp_b200.memory import select_default_device
+
+    if _lib.device_count() == 0:
+        raise RuntimeError("bench.py needs a CUDA device for the GPU arm (no CPU fallback)")
+    select_default_device(local_rank)
+    q = dp.get_default_queue()
+    lib, check = _lib.lib, _lib.check
+    ev = Events(lib, check, q.stream)
+    peak, peak_kind = load_peaks()
+    n = N_OPTIONS
+
+    def barrier():
+        q.wait()
+        if dist is not None:
+            dist.barrier()
+            import torch
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        import torch
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs resident in HBM (each rank prices its own options: weak scaling)
+    dp.random.seed(SEED + rank)
+    price = dp.random.uniform(10.0, 50.0, n)
+    strike = dp.random.uniform(10.0, 50.0, n)
+    tt = dp.random.uniform(1.0, 2.0, n)
+    call = dp.zeros(n, dtype=dp.float64)
+    put = -dp.ones(n, dtype=dp.float64)
+
+    def step():
+        black_scholes(dp, price, strike, tt, RATE, VOL, call, put)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _lib.reset_launch_count()
+    barrier()
+    ms = timed_steps(ev, step, args.steps)
+    barrier()
+    launches = _lib.launch_count()
+    ms = max_over_ranks(ms)
+    ms_per_step = ms / args.steps
+    value = world * n * BYTES_PER_OPTION_CHAIN / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-launch durations of the 26 ufunc kernels (roofline of ew_contig_vec)
+    durations = []
+
+    def hook(nbytes_per_elem, f):
+        e0, e1 = ev.new(), ev.new()
+        ev.record(e0)
+        out = f()
+        ev.record(e1)
+        durations.append((nbytes_per_elem, e0, e1))
+        return out
+
+    passes = 3
+    for _ in range(passes):
+        black_scholes(dp, price, strike, tt, RATE, VOL, call, put, hook=hook)
+    q.wait()
+    tot_ms = sum(ev.elapsed_ms(e0, e1) for _, e0, e1 in durations)
+    tot_bytes = sum(b for b, _, _ in durations) * n
+    achieved = tot_bytes / (tot_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "ew_contig_vec (26 launches per step: f64 unary, binary, array-scalar)",
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "avg_launch_us": tot_ms * 1e3 / len(durations),
+                "algorithmic_bytes_per_launch": tot_bytes / len(durations), "traffic": TRAFFIC_EW_CONTIG_F64}
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: pinned host -> device, chain, device -> pinned host, every step
+    hp = [memory.PinnedHostBuffer(n, "f8") for _ in range(3)]
+    ho = [memory.PinnedHostBuffer(n, "f8") for _ in range(2)]
+    rng = np.random.default_rng(SEED + rank)
+    hp[0].array[:] = rng.uniform(10, 50, n)
+    hp[1].array[:] = rng.uniform(10, 50, n)
+    hp[2].array[:] = rng.uniform(1, 2, n)
+
+    def e2e_step():
+        for dst, src in zip((price, strike, tt), hp):
+            memory.copy_host_to_device(dst, src.array)
+        black_scholes(dp, price, strike, tt, RATE, VOL, call, put)
+        memory.copy_device_to_host(ho[0].array, call)
+        memory.copy_device_to_host(ho[1].array, put)
+        q.wait()
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = ev.new(), ev.new()
+    ev.record(e0)
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev.record(e1)
+    e2e_ms = max_over_ranks(ev.elapsed_ms(e0, e1)) / e2e_steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e = {"value": world * n * BYTES_PER_OPTION_CHAIN / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": 3 * 8 * n, "d2h_bytes_per_step": 2 * 8 * n, "ms_per_step": e2e_ms,
+           "wall_ms_per_step": e2e_wall_ms, "steps": e2e_steps,
+           "checksum": float(ho[0].array[:1024].sum() + ho[1].array[:1024].sum())}
+    for b in hp + ho:
+        b.free()
+
+    # ---- the other configurations
+    ops = []
+    if not args.no_ops:
+        ops = other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, strike, tt, call, put)
+
+    # ---- CPU baseline (rank 0, N=1 only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        try:
+            n_sample = 1 << 24
+            opt_s, reps, total = cpu_chain_throughput(n_sample)
+            cpu = {"value": opt_s * BYTES_PER_OPTION_CHAIN / 1e9, "unit": "GB/s", "cores": cpu_threads(),
+                   "kind": "port",
+                   "sample": f"2^24 of 2^26 options, best of {reps} runs ({total:.1f} s), C chain with libm, OpenMP"}
+        except Exception as exc:  # the checker is optional for the measurement itself
+            cpu = {"value": None, "unit": "GB/s", "cores": cpu_threads(), "kind": "port", "sample": f"failed: {exc}"}
+
+    if rank == 0:
+        line = {
+            "metric": "achieved algorithmic GB/s, Black-Scholes chain (552 B/option)",
+            "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "black_scholes_f64_2^26_chain_26ufuncs_2copies", "options_per_gpu": n,
+                       "rate": RATE, "vol": VOL, "seed": SEED,
+                       "l2": "inputs and temporaries (512 MiB each) exceed the 126 MB L2",
+                       "parallelism": f"shard{world}_no_collective"},
+            "frac_of_peak": value / world / peak, "peak_gbs": peak, "peak_kind": peak_kind,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "ops": ops,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram bytes read+written per launch of ew_contig_vec on f64 operands, from the ncu capture summarised in
+# profiles/ (captured on 2^24 elements and scaled by the element count); None until captured.
+TRAFFIC_EW_CONTIG_F64 = None
+
+
+def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, strike, tt, call, put):
+    """Times the remaining benchmark configurations; returns a list of records."""
+    lib = _lib.lib
+    out = []
+    S = C.c_void_p(q.stream)
+
+    def rec(name, nbytes, ms, kernel=None, note=None):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        r = {"op": name, "ms": ms, "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_peak": gbs / peak,
+             "kernel": kernel or _lib.last_kernel()}
+        if note:
+            r["note"] = note
+        out.append(r)
+
+    n = N_OPTIONS
+    # fused Black-Scholes (one pass)
+    pp, ps, pt = (a.get_array()._ptr for a in (price, strike, tt))
+    pc, pq = call.get_array()._ptr, put.get_array()._ptr
+    ms = median_time_ms(ev, lambda: lib.dpb_black_scholes_f64(n, pp, ps, pt, RATE, VOL, pc, pq, S), 10)
+    rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms, "black_scholes_f64",
+        "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option")
+
+    # C1: add f32 2^24, rotating over 4 buffer sets (768 MiB > L2)
+    m = 1 << 24
+    sets = [(dp.random.uniform(-1, 1, m, dtype="f4"), dp.random.uniform(-1, 1, m, dtype="f4"),
+             dp.empty(m, dtype="f4")) for _ in range(4)]
+    i = [0]
+
+    def c1_api():
+        a, b, o = sets[i[0] & 3]
+        i[0] += 1
+        dp.add(a, b, out=o)
+
+    def c1_abi():
+        a, b, o = sets[i[0] & 3]
+        i[0] += 1
+        lib.dpb_binary_contig(0, 10, 10, 10, m, a.get_array()._ptr, 0, b.get_array()._ptr, 0, o.get_array()._ptr, 0, S)
+
+    ms = median_time_ms(ev, lambda: [c1_api() for _ in range(8)], 10) / 8
+    rec("c1_add_f32_2^24_api", 12 * m, ms, note="8 back-to-back dpnp.add calls per sample, rotating buffers")
+    ms = median_time_ms(ev, lambda: [c1_abi() for _ in range(8)], 10) / 8
+    rec("c1_add_f32_2^24_c_abi", 12 * m, ms)
+    del sets
+
+    # C3: sums of f32 16384 x 65536, rows sharded over the ranks
+    rows, cols = 16384 // world, 65536
+    x = dp.random.normal(0, 1, (rows, cols), dtype="f4")
+    nb = 4 * rows * cols * world
+
+    def time_sharded(fn, reps):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(reps):
+            q.wait()
+            if dist is not None:
+                dist.barrier()
+            e0, e1 = ev.new(), ev.new()
+            ev.record(e0)
+            fn()
+            q.wait()
+            ev.record(e1)
+            t = ev.elapsed_ms(e0, e1)
+            if dist is not None:
+                import torch
+                tt_ = torch.tensor([t], device="cuda", dtype=torch.float64)
+                dist.all_reduce(tt_, op=dist.ReduceOp.MAX)
+                t = float(tt_.item())
+            ts.append(t)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    ms = time_sharded(lambda: dp.sum(x, axis=1), 10)
+    rec("c3a_sum_axis1_f32_16384x65536", nb, ms, note="rows stay whole on one GPU: no exchange")
+
+    def c3b():
+        part = dp.sum(x, axis=0)
+        return sharded.allreduce_sum_ordered(part) if dist is not None else part
+
+    ms = time_sharded(c3b, 10)
+    rec("c3b_sum_axis0_f32_16384x65536", nb, ms, note="partials combined in rank order" if world > 1 else None)
+
+    def c3c():
+        part = dp.sum(x)
+        tot = sharded.allreduce_sum_ordered(part) if dist is not None else part
+        return tot / float(rows * world * cols)
+
+    ms = time_sharded(c3c if world > 1 else (lambda: dp.mean(x)), 10)
+    rec("c3c_mean_f32_16384x65536", nb, ms)
+    del x
+
+    # C4: multiply(a.transpose(2,0,1), b), `a` sharded along its leading axis
+    ja = 1024 // world
+    a = dp.random.uniform(-2, 2, (ja, 4096, 64), dtype="f4")
+    b = dp.random.uniform(-2, 2, (64, 1, 4096), dtype="f4")
+    o = dp.empty((64, ja, 4096), dtype="f4")
+    at = a.transpose(2, 0, 1)
+    ms = time_sharded(lambda: dp.multiply(at, b, out=o), 10)
+    rec("c4_multiply_transposed_broadcast_f32", (2 * ja * 4096 * 64 * 4 + 64 * 4096 * 4) * world, ms)
+    del a, b, o, at
+
+    # C5: max / argmax of int32 (8, 2^29), leading axis sharded
+    r5 = max(1, 8 // world)
+    x = dp.random.randint(0, 1000, (r5, 1 << 29), dtype="i4")
+    nb = 4 * r5 * (1 << 29) * world
+
+    def c5_max():
+        part = dp.max(x)
+        return sharded.allreduce_extreme(part, "max") if dist is not None else part
+
+    def c5_argmax():
+        idx = dp.argmax(x)
+        if dist is None:
+            return idx
+        i_loc = int(idx.asnumpy())
+        v = x.reshape(-1)[i_loc].asnumpy()
+        return sharded.combine_arg_extreme(v, i_loc + rank * r5 * (1 << 29), "max")
+
+    ms = time_sharded(c5_max, 5)
+    rec("c5_max_flat_int32_8x2^29", nb, ms)
+    ms = time_sharded(lambda: dp.max(x, axis=-1), 5)
+    rec("c5_max_lastaxis_int32_8x2^29", nb, ms)
+    ms = time_sharded(c5_argmax, 5)
+    rec("c5_argmax_flat_int32_8x2^29", nb, ms)
+    ms = time_sharded(lambda: dp.argmax(x, axis=-1), 5)
+    rec("c5_argmax_lastaxis_int32_8x2^29", nb, ms)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-configuration extras")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@ namespace dpb {
 // ------------------------------------------------------------------ errors
 int set_error(int status, const char *fmt, ...);
 void note_kernel(const char *name);  // records family name and counts one launch
+void note_copy(const char *name);    // records the name of a library copy (not a kernel of ours)
 int check_launch(const char *what);  // cudaGetLastError -> status
 
 #define DPB_CUDA_TRY(expr)                                                              \

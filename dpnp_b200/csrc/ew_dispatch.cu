@@ -501,7 +501,7 @@ int dpb_copy_array_into_array(const dpb_array *src, const dpb_array *dst, void *
     const bool both_c = (src->flags & DPB_FLAG_C_CONTIGUOUS) && (dst->flags & DPB_FLAG_C_CONTIGUOUS);
     const bool both_f = (src->flags & DPB_FLAG_F_CONTIGUOUS) && (dst->flags & DPB_FLAG_F_CONTIGUOUS);
     if (src->typenum == dst->typenum && (both_c || both_f)) {
-        note_kernel("memcpy_d2d");
+        note_copy("memcpy_d2d");
         return dpb_memcpy(dst->data, src->data, static_cast<size_t>(n) * type_size(src->typenum), 2,
                           stream);
     }

@@ -29,6 +29,8 @@ void note_kernel(const char *name)
     ++g_launches;
 }
 
+void note_copy(const char *name) { g_last_kernel = name; }
+
 int check_launch(const char *what)
 {
     cudaError_t err = cudaGetLastError();

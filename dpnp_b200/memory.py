@@ -21,7 +21,7 @@ from ._lib import check, lib
 
 __all__ = [
     "StreamQueue", "get_default_queue", "MemoryUSMDevice", "MemoryUSMShared", "MemoryUSMHost",
-    "create_data", "pool_stats", "pool_trim", "pool_set_limit", "ExecutionPlacementError",
+    "create_data", "PinnedHostBuffer", "copy_host_to_device", "copy_device_to_host", "pool_stats", "pool_trim", "pool_set_limit", "ExecutionPlacementError",
 ]
 
 
@@ -184,6 +184,63 @@ class MemoryUSMHost(MemoryUSMDevice):
     """Accepted for API compatibility; backed by device memory."""
 
     usm_type = "host"
+
+
+class PinnedHostBuffer:
+    """Page-locked host memory (cudaHostAlloc) viewed as a NumPy array: the staging
+    area for fast host<->device copies."""
+
+    def __init__(self, shape, dtype):
+        import numpy as np
+
+        self.dtype = np.dtype(dtype)
+        self.shape = (int(shape),) if isinstance(shape, int) else tuple(int(s) for s in shape)
+        n = 1
+        for s in self.shape:
+            n *= s
+        self.nbytes = n * self.dtype.itemsize
+        p = C.c_void_p()
+        check(lib.dpb_host_alloc(self.nbytes, C.byref(p)))
+        self._ptr = p.value
+        buf = (C.c_char * max(self.nbytes, 1)).from_address(self._ptr)
+        self.array = np.frombuffer(buf, dtype=self.dtype, count=n).reshape(self.shape)
+
+    def free(self):
+        ptr, self._ptr = self._ptr, 0
+        if ptr:
+            self.array = None
+            try:
+                lib.dpb_host_free(C.c_void_p(ptr))
+            except Exception:
+                pass
+
+    def __del__(self):
+        self.free()
+
+
+def copy_host_to_device(dst, host_array, queue=None):
+    """Enqueue dst[...] = host_array (same dtype, both C-contiguous) without synchronising;
+    the host buffer must stay alive until the queue has been waited on."""
+    u = dst.get_array() if hasattr(dst, "get_array") else dst
+    q = queue or u.sycl_queue
+    if not (u.flags.c_contiguous and host_array.flags.c_contiguous and u.dtype == host_array.dtype
+            and u.size == host_array.size):
+        raise ValueError("copy_host_to_device needs matching C-contiguous buffers")
+    q.activate()
+    check(lib.dpb_memcpy(C.c_void_p(u._ptr), C.c_void_p(host_array.ctypes.data), host_array.nbytes, 0,
+                         C.c_void_p(q.stream)))
+
+
+def copy_device_to_host(host_array, src, queue=None):
+    """Enqueue host_array[...] = src without synchronising."""
+    u = src.get_array() if hasattr(src, "get_array") else src
+    q = queue or u.sycl_queue
+    if not (u.flags.c_contiguous and host_array.flags.c_contiguous and u.dtype == host_array.dtype
+            and u.size == host_array.size):
+        raise ValueError("copy_device_to_host needs matching C-contiguous buffers")
+    q.activate()
+    check(lib.dpb_memcpy(C.c_void_p(host_array.ctypes.data), C.c_void_p(u._ptr), host_array.nbytes, 1,
+                         C.c_void_p(q.stream)))
 
 
 def create_data(x):

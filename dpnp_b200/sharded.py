@@ -1,0 +1,153 @@
+"""Leading-axis sharding of arrays over the GPUs of one box, one process per GPU.
+
+Elementwise work on identically sharded operands needs no communication.  A
+reduction either keeps whole rows on one GPU (no exchange) or produces one
+partial result per rank that is combined in a single step:
+
+* sum over the sharded axis / over everything: all-gather of the partials and
+  a local sum in rank order, so every rank gets bit-identical results that do
+  not depend on the collective's internal ordering;
+* max / min: all-reduce with MAX / MIN;
+* argmax / argmin over everything: all-gather of (value, global flat index)
+  pairs, then the first-occurrence rule (better value; ties -> smaller index).
+
+The reference has no multi-device execution (arrays are tied to one queue,
+dpnp/tensor/_compute_follows_data.pyx:67-160); this module is new functionality.
+``torch.distributed`` provides the process group: NCCL over NVLink for device
+arrays, gloo for host arrays (used by the CPU tests of this logic).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def shard_bounds(n: int, world_size: int, rank: int) -> tuple[int, int]:
+    """Half-open range of leading-axis indices owned by `rank` (sizes differ by at most one)."""
+    base, extra = divmod(int(n), int(world_size))
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def _dist():
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        raise RuntimeError("torch.distributed is not initialised")
+    return dist
+
+
+def _to_torch(x):
+    """(torch tensor sharing memory with x, is_device)."""
+    import torch
+
+    if isinstance(x, np.ndarray):
+        return torch.from_numpy(np.ascontiguousarray(x)), False
+    arr = x.get_array() if hasattr(x, "get_array") else x
+    if not arr.flags.c_contiguous:
+        raise ValueError("collectives need C-contiguous device arrays")
+    arr.sycl_queue.wait()  # the collective runs on torch's stream
+    dt = arr.dtype
+    if dt.kind == "u" and dt.itemsize > 1:
+        # torch has no wide unsigned collectives: move the bits as signed integers of the same size
+        import dpnp_b200.tensor as dpt
+        arr = dpt.usm_ndarray._view(arr.usm_data, arr._ptr, arr.shape, arr.strides, np.dtype(f"i{dt.itemsize}"),
+                                    arr.sycl_queue)
+    return torch.as_tensor(arr, device=f"cuda:{arr.sycl_queue.device}"), True
+
+
+def _gather(x, group=None):
+    """List of every rank's `x` (as NumPy arrays for host input, torch device tensors otherwise)."""
+    import torch
+
+    dist = _dist()
+    t, on_device = _to_torch(x)
+    t = t.reshape(-1) if t.dim() == 0 else t
+    outs = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(outs, t, group=group)
+    if on_device:
+        torch.cuda.synchronize()
+    return outs, on_device
+
+
+def allreduce_sum_ordered(partial, group=None):
+    """Sum of the ranks' partials, added in rank order on every rank."""
+    outs, on_device = _gather(partial, group)
+    if not on_device:
+        acc = outs[0].numpy().copy()
+        for o in outs[1:]:
+            acc = acc + o.numpy()
+        return acc.reshape(np.shape(partial))
+    import dpnp_b200 as dp
+
+    acc = None
+    for o in outs:
+        part = dp.asarray(_torch_to_dpnp(o, partial))
+        acc = part if acc is None else acc + part
+    return acc.reshape(partial.shape)
+
+
+def _torch_to_dpnp(t, like):
+    """Copy a torch device tensor into a new array of the library (device-to-device)."""
+    import ctypes as C
+
+    import dpnp_b200 as dp
+    from dpnp_b200._lib import check, lib
+
+    out = dp.empty(tuple(t.shape), dtype=like.dtype)
+    q = out.sycl_queue
+    q.activate()
+    check(lib.dpb_memcpy(C.c_void_p(out.get_array()._ptr), C.c_void_p(t.data_ptr()), out.nbytes, 2,
+                         C.c_void_p(q.stream)))
+    q.wait()
+    return out
+
+
+def allreduce_extreme(partial, op="max", group=None):
+    """Elementwise max/min of the ranks' partials (in place for device arrays)."""
+    import torch
+
+    dist = _dist()
+    t, on_device = _to_torch(partial)
+    red = dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.MIN
+    dist.all_reduce(t, op=red, group=group)
+    if on_device:
+        torch.cuda.synchronize()
+        return partial
+    return t.numpy().reshape(np.shape(partial))
+
+
+def combine_arg_extreme(value, global_index, op="max", group=None):
+    """Global argmax/argmin from each rank's (extreme value, global flat index of its first
+    occurrence).  Inputs are host scalars/0-d arrays; returns (value, index) as NumPy scalars."""
+    import torch
+
+    dist = _dist()
+    world = dist.get_world_size(group)
+    v = np.asarray(value)
+    pair = np.zeros(2, dtype=np.float64 if v.dtype.kind == "f" else np.int64)
+    if v.dtype.kind == "f":
+        # indices below 2^53 are exact in float64
+        pair[0], pair[1] = float(v), float(int(global_index))
+    else:
+        pair[0], pair[1] = int(v), int(global_index)
+    t = torch.from_numpy(pair)
+    backend = dist.get_backend(group)
+    if backend == "nccl":
+        t = t.cuda()
+    outs = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(outs, t, group=group)
+    pairs = np.stack([o.cpu().numpy() for o in outs])
+    best = 0
+    for r in range(1, world):
+        a, b = pairs[r], pairs[best]
+        a_nan, b_nan = a[0] != a[0], b[0] != b[0]
+        if a_nan or b_nan:
+            better = a_nan and (not b_nan or a[1] < b[1])
+        elif a[0] == b[0]:
+            better = a[1] < b[1]
+        else:
+            better = a[0] > b[0] if op == "max" else a[0] < b[0]
+        if better:
+            best = r
+    return v.dtype.type(pairs[best][0]), np.int64(pairs[best][1])

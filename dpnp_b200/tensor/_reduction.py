@@ -10,6 +10,8 @@ and argmax/argmin accept an integer axis or None only (:309-316).
 
 from __future__ import annotations
 
+import builtins
+
 import numpy as np
 
 from ..memory import ExecutionPlacementError
@@ -121,7 +123,7 @@ def _comparison_over_axis(x, axis, keepdims, out, _reduction_fn):
     nd = x.ndim
     arr, axis, perm = _permute_reduced_last(x, axis)
     red_nd = len(axis)
-    if any(arr.shape[i] == 0 for i in range(nd - red_nd, nd)):
+    if builtins.any(arr.shape[i] == 0 for i in range(nd - red_nd, nd)):
         raise ValueError("reduction cannot be performed over zero-size axes")
     res_shape = arr.shape[: nd - red_nd]
     q = x.sycl_queue
@@ -152,7 +154,7 @@ def _search_over_axis(x, axis, keepdims, out, _reduction_fn):
     nd = x.ndim
     arr, axis, perm = _permute_reduced_last(x, axis, int_axis_only=True)
     red_nd = len(axis)
-    if any(arr.shape[i] == 0 for i in range(nd - red_nd, nd)):
+    if builtins.any(arr.shape[i] == 0 for i in range(nd - red_nd, nd)):
         raise ValueError("reduction cannot be performed over zero-size axes")
     res_shape = arr.shape[: nd - red_nd]
     q = x.sycl_queue

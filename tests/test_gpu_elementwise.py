@@ -64,10 +64,14 @@ def test_binary_dtype_matrix_is_bit_exact(op, dt):
     exp = orc.binary_result(op, x, y)
     got = getattr(dp, op)(dev(x), dev(y)).asnumpy()
     assert got.dtype == exp.dtype
-    if op == "divide" and np.dtype(dt).kind in "biu":
-        # integers are promoted to float64 first; the division itself is exact IEEE
-        np.testing.assert_array_equal(got, exp)
+    if op == "multiply" and np.dtype(dt).kind == "c":
+        # (ac - bd) + (ad + bc)i: each product and sum rounds on its own here, while the host
+        # library may fuse a multiply-add; the two differ by one rounding of a part
+        eps = np.finfo(exp.real.dtype).eps
+        scale = np.abs(x) * np.abs(y)
+        assert np.all(np.abs(got - exp) <= 2 * eps * scale)
     else:
+        # (integer division promotes to float64 first; the division itself is exact IEEE)
         np.testing.assert_array_equal(got, exp)
 
 
