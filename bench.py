@@ -546,6 +546,55 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     return out
 
 
+PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "sum_axis1",
+                 "sum_axis0", "mean_all", "transpose_c4", "max_i32", "argmax_i32")
+
+
+def profile_case(name, launches=3):
+    """Run one kernel a few times on a small input (larger than L2, about 1 GB on the device):
+    the command line an ncu capture of that kernel is made with."""
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    q = dp.get_default_queue()
+    if name == "ew_add_f32":
+        n = 1 << 26
+        a, b, o = dp.random.uniform(-1, 1, n, dtype="f4"), dp.random.uniform(-1, 1, n, dtype="f4"), dp.empty(n, dtype="f4")
+        fn = lambda: dp.add(a, b, out=o)
+    elif name in ("ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64"):
+        n = 1 << 25
+        a, b, o = dp.random.uniform(-1, 1, n), dp.random.uniform(-1, 1, n), dp.empty(n)
+        fn = {"ew_mul_f64": lambda: dp.multiply(a, b, out=o), "ew_mul_scalar_f64": lambda: dp.multiply(a, 0.25, out=o),
+              "ew_erf_f64": lambda: dp.erf(a, out=o)}[name]
+    elif name == "bs_fused":
+        n = 1 << 24
+        p, s, t = dp.random.uniform(10, 50, n), dp.random.uniform(10, 50, n), dp.random.uniform(1, 2, n)
+        c, u = dp.empty(n), dp.empty(n)
+        S = C.c_void_p(q.stream)
+        fn = lambda: _lib.lib.dpb_black_scholes_f64(n, p.get_array()._ptr, s.get_array()._ptr, t.get_array()._ptr,
+                                                    RATE, VOL, c.get_array()._ptr, u.get_array()._ptr, S)
+    elif name in ("sum_axis1", "sum_axis0", "mean_all"):
+        x = dp.random.normal(0, 1, (4096, 65536), dtype="f4")
+        fn = {"sum_axis1": lambda: dp.sum(x, axis=1), "sum_axis0": lambda: dp.sum(x, axis=0),
+              "mean_all": lambda: dp.mean(x)}[name]
+    elif name == "transpose_c4":
+        a = dp.random.uniform(-2, 2, (128, 4096, 64), dtype="f4")
+        b = dp.random.uniform(-2, 2, (64, 1, 4096), dtype="f4")
+        o = dp.empty((64, 128, 4096), dtype="f4")
+        at = a.transpose(2, 0, 1)
+        fn = lambda: dp.multiply(at, b, out=o)
+    elif name in ("max_i32", "argmax_i32"):
+        x = dp.random.randint(0, 1000, (8, 1 << 25), dtype="i4")
+        fn = (lambda: dp.max(x, axis=-1)) if name == "max_i32" else (lambda: dp.argmax(x, axis=-1))
+    else:
+        raise SystemExit(f"unknown profile case {name}; choose from {PROFILE_CASES}")
+    q.wait()
+    for _ in range(launches):
+        fn()
+    q.wait()
+    print(json.dumps({"profile_case": name, "launches": launches, "kernel": _lib.last_kernel()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -554,8 +603,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-configuration extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None, help="run one small case for an ncu capture: "
+                    + ", ".join(PROFILE_CASES))
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -1,6 +1,6 @@
 """In-tree build of libdpnp_b200.so with nvcc for sm_100a.
 
-``python -m dpnp_b200._build`` compiles every source under ``csrc/`` into an
+``python dpnp_b200/_build.py`` compiles every source under ``csrc/`` into an
 object file (in parallel, skipping objects newer than all sources and headers)
 and links them into ``dpnp_b200/libdpnp_b200.so``.  The CUDA runtime is linked
 statically, so the library needs only the driver at run time.

@@ -77,7 +77,7 @@ class dpb_array(C.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m dpnp_b200._build` "
+            f"{LIB_PATH} is missing: build it with `python dpnp_b200/_build.py` "
             "(there is no CPU fallback)"
         )
     return C.CDLL(LIB_PATH)
@@ -158,7 +158,11 @@ PROTOTYPES = {
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():
-    _fn = getattr(lib, _name)  # AttributeError here means the library is stale
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError:
+        raise ImportError(f"{LIB_PATH} does not export {_name}: it is older than the sources, rebuild it "
+                          "with `python dpnp_b200/_build.py`") from None
     _fn.restype = _res
     _fn.argtypes = _args
 

@@ -45,8 +45,9 @@ def test_c2_black_scholes_chain_and_fused():
     dpp, dk, dt_ = dev(p), dev(k), dev(t)
     _lib.reset_launch_count()
     call, put = bs_chain_device(dp, dpp, dk, dt_, 0.1, 0.2)
-    # 26 ufunc kernels of the chain, a fill and a negation for `put = -ones`, 2 copies for call[:]/put[:]
-    assert _lib.launch_count() == 30
+    # 26 ufunc kernels of the chain, a fill and a negation for `put = -ones`; the two copies are
+    # library memcpys and are not counted
+    assert _lib.launch_count() == 28
     fc, fp = dp.empty(n), dp.empty(n)
     q = fc.sycl_queue
     _lib.check(_lib.lib.dpb_black_scholes_f64(n, dpp.get_array()._ptr, dk.get_array()._ptr, dt_.get_array()._ptr,
