@@ -412,9 +412,10 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-# dram bytes read+written per launch of ew_contig_vec on f64 operands, from the ncu capture summarised in
-# profiles/ (captured on 2^24 elements and scaled by the element count); None until captured.
-TRAFFIC_EW_CONTIG_F64 = None
+# dram bytes read+written per launch of ew_contig_vec on 2^26 f64 operands: the ncu capture summarised in
+# profiles/ew_contig_vec_f64_multiply_2p25.md measured 0.95 x the algorithmic bytes on 2^25 elements; scaled
+# by the element count and averaged over the step's 10 array-array and 16 unary/array-scalar launches.
+TRAFFIC_EW_CONTIG_F64 = 1.22e9
 
 
 def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, strike, tt, call, put):
