@@ -132,6 +132,7 @@ PROTOTYPES = {
     "dpb_copy_cast_strided": (_i, [_i, _i, _i64, _i, _pi64, _vp, _i64, _vp, _i64, _vp]),
     "dpb_reduce_axis1_contig": (_i, [_i, _i, _i, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "dpb_reduce_axis0_contig": (_i, [_i, _i, _i, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
+    "dpb_reduce_axis1_contig_noalloc": (_i, [_i, _i, _i, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "dpb_reduce_strided": (_i, [_i, _i, _i, _i64, _i64, _vp, _vp, _i, _pi64, _i64, _i64, _i, _pi64, _i64, _vp]),
     "dpb_search_axis1_contig": (_i, [_i, _i, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "dpb_search_axis0_contig": (_i, [_i, _i, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),

@@ -321,6 +321,29 @@ int dpb_reduce_strided(int op, int t_in, int t_out, int64_t iter_nelems, int64_t
                        const void *arg, void *res, int iter_nd, const int64_t *iter_shape_strides,
                        int64_t iter_arg_off, int64_t iter_res_off, int red_nd,
                        const int64_t *red_shape_strides, int64_t red_arg_off, void *stream);
+/* Same result as dpb_reduce_axis1_contig for sum, max and min over rows of int32,
+ * int64, float32 or float64 (plus int32 summed into int64), but the call obtains no
+ * memory from CUDA or from the pool.  It exists for callers that may not allocate while
+ * they run: code hosted by a framework whose own allocator already owns the device,
+ * services held to a fixed memory budget, loops whose latency must not depend on the
+ * pool growing.  It has no counterpart in the reference, whose reductions always take
+ * their temporaries from sycl::malloc_device.
+ *
+ * Long rows are split over several blocks; their partial results go to a 64 KiB array
+ * that is part of the library image (one copy per GPU that loads the library, held until
+ * the process exits).  With the default launch geometry the partials of any shape fit
+ * (at most about 2 * SMs * 8 of them, 16 bytes each).  A reduction whose partials would
+ * not fit -- rows * splits * accumulator size > 64 KiB, which takes a raised
+ * "ctas_per_sm" tuning value -- is refused with DPB_ERR_VALUE and a message naming both
+ * sizes; unsupported type pairs give
+ * DPB_ERR_RUNTIME.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before starting
+ * any stream capture.  All calls share the one array, which keeps whatever the previous
+ * call left there: nothing needs clearing, because every partial is written before it is
+ * read, but two calls that overlap on the GPU (different streams) race on it. */
+int dpb_reduce_axis1_contig_noalloc(int op, int t_in, int t_out, int64_t iter_nelems,
+                                    int64_t reduction_nelems, const void *arg, int64_t arg_off,
+                                    void *res, int64_t res_off, void *stream);
 /* Search reductions; result type is always int64, the index is the C-order
  * position inside the reduced sub-space, ties resolve to the smallest index
  * and a NaN is an extreme value.  Replaces search_axis1/axis0_over_group_temps_contig_impl
