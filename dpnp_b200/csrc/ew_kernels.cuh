@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kEwThreads)
 template <class F, int VEC, int UNROLL>
 __global__ void __launch_bounds__(kEwThreads)
     ew_rows_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> outer, int64_t L, unsigned inner_bcast,
-                   int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork)
+                   int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div)
 {
     using In0 = typename F::In0;
     using In1 = typename F::In1;
@@ -146,7 +146,9 @@ __global__ void __launch_bounds__(kEwThreads)
     const int ty = threadIdx.x >> tx_log2;
 
     for (int64_t w = blockIdx.x; w < nwork; w += gridDim.x) {
-        const int64_t rg = w / chunks_per_row;
+        // 31-bit multiply-shift division when the work count allows it
+        const int64_t rg = (nwork < (int64_t(1) << 31)) ? int64_t(chunk_div.div(static_cast<uint32_t>(w)))
+                                                         : w / chunks_per_row;
         const int64_t chunk = w - rg * chunks_per_row;
         const int64_t row = rg * TY + ty;
         if (row >= nrows) continue;
@@ -306,6 +308,173 @@ __global__ void __launch_bounds__(kTile *kTileRows)
     }
 }
 
+// Vector form of the transpose kernel for operands of one element size (4 or 8
+// bytes): the tile is T x T elements with T = 16 * VEC, staged inputs are read
+// with 16-byte loads along P, every other input and the output with 16-byte
+// accesses along Q.  Rows of the tile are padded by one element, which keeps the
+// transposing shared-memory accesses at most 2-way conflicted.
+struct TransposeStrides {
+    int64_t sp[3];  // input strides along P
+    int64_t sq[3];  // input strides along Q
+    int64_t spo;    // output stride along P (its stride along Q is 1)
+};
+
+// Tile coordinates of work item w and the operands' batch offsets (31-bit
+// multiply-shift divisions: the launcher guarantees nwork < 2^31).
+struct TileDivs {
+    FastDiv32 per_batch;  // tiles_p * tiles_q
+    FastDiv32 per_row;    // tiles_q
+};
+
+template <class F>
+DPB_D void transpose_tile_origin(const StridedMeta<F::NIN + 1> &batch, const TileDivs &td, uint32_t w, int T,
+                                 int64_t &p0, int64_t &q0, int64_t (&off)[F::NIN + 1])
+{
+    constexpr int NARR = F::NIN + 1;
+    uint32_t bi, tw, tp, tq;
+    td.per_batch.divmod(w, bi, tw);
+    td.per_row.divmod(tw, tp, tq);
+    p0 = int64_t(tp) * T;
+    q0 = int64_t(tq) * T;
+#pragma unroll
+    for (int k = 0; k < NARR; ++k) off[k] = 0;
+    uint32_t rem = bi;
+    for (int d = batch.nd - 1; d >= 0; --d) {
+        uint32_t q, r;
+        batch.div[d].divmod(rem, q, r);
+        rem = q;
+#pragma unroll
+        for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * batch.strides[k][d];
+    }
+}
+
+// A block works through `tiles_per_block` consecutive tiles; the 16-byte loads
+// of the next tile's staged inputs are issued before the current tile is
+// combined and stored, so global loads stay in flight across the barriers.
+template <class F, int VEC>
+__global__ void __launch_bounds__(kEwThreads)
+    ew_transpose_vec_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> batch, int64_t np, int64_t nq,
+                            TransposeStrides st, unsigned staged, unsigned vecq, TileDivs td,
+                            uint32_t nwork, int tiles_per_block)
+{
+    using In0 = typename F::In0;
+    using In1 = typename F::In1;
+    using In2 = typename F::In2;
+    using Out = typename F::Out;
+    constexpr int NARR = F::NIN + 1;
+    constexpr int T = 16 * VEC;
+    __shared__ In0 s0[F::NIN >= 1 ? T : 1][T + 1];
+    __shared__ In1 s1[F::NIN >= 2 ? T : 1][T + 1];
+
+    const int lane16 = threadIdx.x & 15;  // vector index inside a tile row
+    const int row16 = threadIdx.x >> 4;   // 0..15
+    const uint32_t w_begin = blockIdx.x * static_cast<uint32_t>(tiles_per_block);
+    uint32_t w_end = w_begin + static_cast<uint32_t>(tiles_per_block);
+    if (w_end > nwork || w_end < w_begin) w_end = nwork;
+
+    vec_t<In0, VEC> ra[VEC];
+    vec_t<In1, VEC> rb[VEC];
+
+    // issue the staged loads of tile w into registers
+    auto prefetch = [&](uint32_t w) {
+        int64_t p0, q0, off[NARR];
+        transpose_tile_origin<F>(batch, td, w, T, p0, q0, off);
+        const int64_t pp = p0 + lane16 * VEC;
+#pragma unroll
+        for (int r = 0; r < VEC; ++r) {
+            const int64_t qq = q0 + row16 + 16 * r;
+            if (pp < np && qq < nq) {
+                if constexpr (F::NIN >= 1) {
+                    if (staged & 1u)
+                        ra[r] = load_vec<vec_t<In0, VEC>>(static_cast<const In0 *>(p.in[0]) + off[0] + pp +
+                                                          qq * st.sq[0]);
+                }
+                if constexpr (F::NIN >= 2) {
+                    if (staged & 2u)
+                        rb[r] = load_vec<vec_t<In1, VEC>>(static_cast<const In1 *>(p.in[1]) + off[1] + pp +
+                                                          qq * st.sq[1]);
+                }
+            }
+        }
+    };
+
+    if (w_begin < w_end) prefetch(w_begin);
+    for (uint32_t w = w_begin; w < w_end; ++w) {
+        // registers -> transposed tile
+#pragma unroll
+        for (int r = 0; r < VEC; ++r) {
+            const int qi = row16 + 16 * r;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                if constexpr (F::NIN >= 1) { if (staged & 1u) s0[lane16 * VEC + e][qi] = ra[r].v[e]; }
+                if constexpr (F::NIN >= 2) { if (staged & 2u) s1[lane16 * VEC + e][qi] = rb[r].v[e]; }
+            }
+        }
+        __syncthreads();
+        if (w + 1 < w_end) prefetch(w + 1);
+
+        int64_t p0, q0, off[NARR];
+        transpose_tile_origin<F>(batch, td, w, T, p0, q0, off);
+        const In0 *a = static_cast<const In0 *>(p.in[0]) + (F::NIN >= 1 ? off[0] : 0);
+        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
+        const In2 *c = static_cast<const In2 *>(p.in[2]) + (F::NIN >= 3 ? off[2] : 0);
+        Out *o = static_cast<Out *>(p.out) + off[NARR - 1];
+        const int64_t qq = q0 + lane16 * VEC;
+#pragma unroll
+        for (int r = 0; r < VEC; ++r) {
+            const int pi = row16 + 16 * r;
+            const int64_t pp = p0 + pi;
+            if (pp < np && qq < nq) {
+                vec_t<In0, VEC> x;
+                vec_t<In1, VEC> y;
+                vec_t<In2, VEC> z;
+                if constexpr (F::NIN >= 1) {
+                    if (staged & 1u) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) x.v[e] = s0[pi][lane16 * VEC + e];
+                    }
+                    else if (vecq & 1u) x = load_vec<vec_t<In0, VEC>>(a + pp * st.sp[0] + qq);
+                    else {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) x.v[e] = a[pp * st.sp[0] + (qq + e) * st.sq[0]];
+                    }
+                }
+                if constexpr (F::NIN >= 2) {
+                    if (staged & 2u) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) y.v[e] = s1[pi][lane16 * VEC + e];
+                    }
+                    else if (vecq & 2u) y = load_vec<vec_t<In1, VEC>>(b + pp * st.sp[1] + qq);
+                    else {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) y.v[e] = b[pp * st.sp[1] + (qq + e) * st.sq[1]];
+                    }
+                }
+                if constexpr (F::NIN >= 3) {
+                    if (vecq & 4u) z = load_vec<vec_t<In2, VEC>>(c + pp * st.sp[2] + qq);
+                    else {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) z.v[e] = c[pp * st.sp[2] + (qq + e) * st.sq[2]];
+                    }
+                }
+                vec_t<Out, VEC> res;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    In0 xe{};
+                    In1 ye{};
+                    In2 ze{};
+                    if constexpr (F::NIN >= 1) xe = x.v[e];
+                    if constexpr (F::NIN >= 2) ye = y.v[e];
+                    if constexpr (F::NIN >= 3) ze = z.v[e];
+                    res.v[e] = ew_apply(f, xe, ye, ze);
+                }
+                store_vec(o + pp * st.spo + qq, res);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------- generic
 template <class F, bool IDX32, int UNROLL>
 __global__ void __launch_bounds__(kEwThreads)
@@ -375,6 +544,15 @@ inline void fill_meta(StridedMeta<NARR> &m, const EwPlan &plan, const int *dims,
     }
 }
 
+// One block per tile (the hardware scheduler balances the tail better than a
+// fixed grid-stride partition); the kernels keep their stride loops, so a grid
+// capped at 2^30 blocks still covers any size.
+inline int ew_flat_grid(int64_t ntiles)
+{
+    const int64_t cap = int64_t(1) << 30;
+    return static_cast<int>(ntiles < 1 ? 1 : (ntiles < cap ? ntiles : cap));
+}
+
 inline int ew_grid(int64_t nwork)
 {
     const int64_t cap = int64_t(device_props().sm_count) * tuning_ctas_per_sm();
@@ -409,14 +587,14 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
             constexpr int UNROLL = 4;
             const int64_t tiles = plan.n / (int64_t(kEwThreads) * VEC * UNROLL);
             ew_contig_vec_kernel<F, VEC, UNROLL>
-                <<<ew_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
+                <<<ew_flat_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
             note_kernel("ew_contig_vec");
         }
         else {
             constexpr int UNROLL = 4;
             const int64_t tiles = plan.n / (int64_t(kEwThreads) * UNROLL);
             ew_contig_vec_kernel<F, 1, UNROLL>
-                <<<ew_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
+                <<<ew_flat_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
             note_kernel("ew_contig_scalar");
         }
         return check_launch("ew_contig");
@@ -449,14 +627,15 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         const int TX = 1 << tx_log2, TY = kEwThreads >> tx_log2;
         const int64_t chunks = ceil_div(nvec, int64_t(TX) * UNROLL);
         const int64_t nwork = ceil_div(nrows, TY) * chunks;
+        const FastDiv32 chunk_div(static_cast<uint32_t>(chunks < (int64_t(1) << 31) ? chunks : 1));
         if (vec > 1) {
-            ew_rows_kernel<F, VEC, UNROLL><<<ew_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork);
+            ew_rows_kernel<F, VEC, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div);
             note_kernel("ew_rows_vec");
         }
         else {
-            ew_rows_kernel<F, 1, UNROLL><<<ew_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork);
+            ew_rows_kernel<F, 1, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div);
             note_kernel("ew_rows_scalar");
         }
         return check_launch("ew_rows");
@@ -476,6 +655,52 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
             StridedMeta<NARR> batch;
             fill_meta(batch, plan, dims, nb, arr_index);
             const int64_t np = plan.shape[pd], nq = plan.shape[q];
+            // vector form: one element size (4 or 8 bytes) everywhere, at most the first two
+            // inputs staged, every vector access 16-byte aligned
+            if constexpr (NIN >= 1 && (sizeof(Out) == 4 || sizeof(Out) == 8) &&
+                          (NIN < 1 || sizeof(typename F::In0) == sizeof(Out)) &&
+                          (NIN < 2 || sizeof(typename F::In1) == sizeof(Out)) &&
+                          (NIN < 3 || sizeof(typename F::In2) == sizeof(Out))) {
+                constexpr int TV = 16 / static_cast<int>(sizeof(Out));
+                bool ok = !(plan.staged_mask & 4u) && np % TV == 0 && nq % TV == 0 && is_aligned(out, 16) &&
+                          plan.strides[NARR - 1][pd] % TV == 0 &&
+                          nbatch * ceil_div(np, 16 * TV) * ceil_div(nq, 16 * TV) < (int64_t(1) << 31);
+                for (int i = 0; i < nb && ok; ++i) ok = plan.strides[NARR - 1][dims[i]] % TV == 0;
+                unsigned vecq = 0;
+                for (int k = 0; k < NIN && ok; ++k) {
+                    bool aligned_k = is_aligned(in[k], 16);
+                    for (int i = 0; i < nb; ++i) aligned_k = aligned_k && plan.strides[k][dims[i]] % TV == 0;
+                    if (plan.staged_mask & (1u << k)) {
+                        ok = aligned_k && plan.strides[k][q] % TV == 0;
+                    }
+                    else if (plan.strides[k][q] == 1 && aligned_k && plan.strides[k][pd] % TV == 0) {
+                        vecq |= (1u << k);
+                    }
+                }
+                if (ok) {
+                    constexpr int T = 16 * TV;
+                    TransposeStrides ts;
+                    for (int k = 0; k < 3; ++k) {
+                        ts.sp[k] = k < NIN ? plan.strides[k][pd] : 0;
+                        ts.sq[k] = k < NIN ? plan.strides[k][q] : 0;
+                    }
+                    ts.spo = plan.strides[NARR - 1][pd];
+                    const int64_t tp = ceil_div(np, T), tq = ceil_div(nq, T);
+                    const int64_t nw = nbatch * tp * tq;
+                    // consecutive tiles per block (so loads can run ahead), many blocks per SM
+                    const int tpb = nw >= int64_t(device_props().sm_count) * 64 ? 8 : 1;
+                    const int64_t nblocks = ceil_div(nw, tpb);
+                    if (nblocks > 0x7fffffffLL)
+                        return set_error(DPB_ERR_RUNTIME, "iteration space too large for the tiled kernel");
+                    TileDivs td;
+                    td.per_batch = FastDiv32(static_cast<uint32_t>(tp * tq));
+                    td.per_row = FastDiv32(static_cast<uint32_t>(tq));
+                    ew_transpose_vec_kernel<F, TV><<<static_cast<unsigned>(nblocks), kEwThreads, 0, stream>>>(
+                        f, p, batch, np, nq, ts, plan.staged_mask, vecq, td, static_cast<uint32_t>(nw), tpb);
+                    note_kernel("ew_transpose_vec");
+                    return check_launch("ew_transpose_vec");
+                }
+            }
             const int64_t tiles_p = ceil_div(np, kTile), tiles_q = ceil_div(nq, kTile);
             const int64_t nwork = nbatch * tiles_p * tiles_q;
             auto sp = [&](int k) { return k < NIN ? plan.strides[k][pd] : 0; };

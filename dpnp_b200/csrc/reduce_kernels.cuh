@@ -164,38 +164,63 @@ __global__ void __launch_bounds__(kRedThreads)
                 if (t < head) acc = R::step(acc, p[t], begin + t);
                 const In *q = p + head;
                 const int64_t nvec = (len - head) / VEC;
-                // independent accumulators per load slot only while they stay cheap
-                constexpr int LU = (sizeof(Acc) * VEC * UNROLL <= 256) ? UNROLL : 1;
-                Acc lanes[LU][VEC];
+                if constexpr (R::kVectorStep) {
+                    // one accumulator per load slot, fed a whole vector at a time
+                    Acc la[UNROLL];
 #pragma unroll
-                for (int u = 0; u < LU; ++u)
+                    for (int u = 0; u < UNROLL; ++u) la[u] = R::identity();
+                    int64_t v = t;
+                    for (; v + int64_t(UNROLL - 1) * GROUP < nvec; v += int64_t(UNROLL) * GROUP) {
+                        vec_t<In, VEC> x[UNROLL];
 #pragma unroll
-                    for (int k = 0; k < VEC; ++k) lanes[u][k] = R::identity();
-                int64_t v = t;
-                for (; v + int64_t(UNROLL - 1) * GROUP < nvec; v += int64_t(UNROLL) * GROUP) {
-                    vec_t<In, VEC> x[UNROLL];
+                        for (int u = 0; u < UNROLL; ++u)
+                            x[u] = load_vec<vec_t<In, VEC>>(q + (v + int64_t(u) * GROUP) * VEC);
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u)
-                        x[u] = load_vec<vec_t<In, VEC>>(q + (v + int64_t(u) * GROUP) * VEC);
+                        for (int u = 0; u < UNROLL; ++u)
+                            la[u] = R::template step_vec<VEC>(la[u], x[u].v,
+                                                               begin + head + (v + int64_t(u) * GROUP) * VEC);
+                    }
+                    for (; v < nvec; v += GROUP) {
+                        vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(q + v * VEC);
+                        la[0] = R::template step_vec<VEC>(la[0], x.v, begin + head + v * VEC);
+                    }
 #pragma unroll
-                    for (int u = 0; u < UNROLL; ++u) {
-                        const int64_t e0 = begin + head + (v + int64_t(u) * GROUP) * VEC;
+                    for (int u = 0; u < UNROLL; ++u) acc = R::combine(acc, la[u]);
+                }
+                else {
+                    // independent accumulators per load slot only while they stay cheap
+                    constexpr int LU = (sizeof(Acc) * VEC * UNROLL <= 256) ? UNROLL : 1;
+                    Acc lanes[LU][VEC];
+#pragma unroll
+                    for (int u = 0; u < LU; ++u)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) lanes[u][k] = R::identity();
+                    int64_t v = t;
+                    for (; v + int64_t(UNROLL - 1) * GROUP < nvec; v += int64_t(UNROLL) * GROUP) {
+                        vec_t<In, VEC> x[UNROLL];
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u)
+                            x[u] = load_vec<vec_t<In, VEC>>(q + (v + int64_t(u) * GROUP) * VEC);
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const int64_t e0 = begin + head + (v + int64_t(u) * GROUP) * VEC;
+#pragma unroll
+                            for (int k = 0; k < VEC; ++k)
+                                lanes[u % LU][k] = R::step(lanes[u % LU][k], x[u].v[k], e0 + k);
+                        }
+                    }
+                    for (; v < nvec; v += GROUP) {
+                        vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(q + v * VEC);
+                        const int64_t e0 = begin + head + v * VEC;
 #pragma unroll
                         for (int k = 0; k < VEC; ++k)
-                            lanes[u % LU][k] = R::step(lanes[u % LU][k], x[u].v[k], e0 + k);
+                            lanes[0][k] = R::step(lanes[0][k], x.v[k], e0 + k);
                     }
+#pragma unroll
+                    for (int u = 0; u < LU; ++u)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) acc = R::combine(acc, lanes[u][k]);
                 }
-                for (; v < nvec; v += GROUP) {
-                    vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(q + v * VEC);
-                    const int64_t e0 = begin + head + v * VEC;
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k)
-                        lanes[0][k] = R::step(lanes[0][k], x.v[k], e0 + k);
-                }
-#pragma unroll
-                for (int u = 0; u < LU; ++u)
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k) acc = R::combine(acc, lanes[u][k]);
                 const int64_t done = head + nvec * VEC;
                 if (done + t < len) acc = R::step(acc, p[done + t], begin + done + t);
             }

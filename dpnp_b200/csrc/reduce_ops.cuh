@@ -50,6 +50,7 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct SumRed {
     using Acc = TAcc;
     using Out = TOut;
     using Stage2 = SumRed<Acc, TOut, Acc>;
+    static constexpr bool kVectorStep = false;
     static DPB_D Acc identity()
     {
         if constexpr (is_cplx_v<Acc>) return Acc(0, 0);
@@ -72,6 +73,7 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ProdRed {
     using Acc = TAcc;
     using Out = TOut;
     using Stage2 = ProdRed<Acc, TOut, Acc>;
+    static constexpr bool kVectorStep = false;
     static DPB_D Acc identity()
     {
         if constexpr (is_cplx_v<Acc>) return Acc(1, 0);
@@ -96,6 +98,7 @@ template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struc
     using Acc = TAcc;
     using Out = TOut;
     using Stage2 = ExtremeRed<IS_MAX, Acc, TOut, Acc>;
+    static constexpr bool kVectorStep = false;
     static DPB_D Acc identity() { return IS_MAX ? lowest_value<Acc>() : highest_value<Acc>(); }
     static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
     static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
@@ -143,6 +146,8 @@ struct SearchRed {
     using Acc = ValIdx<V>;
     using Out = int64_t;
     using Stage2 = SearchRed<IS_MAX, TIn, V, true>;
+    // one accumulator per group of adjacent elements: see step_vec
+    static constexpr bool kVectorStep = !STAGE2;
     // The identity carries the largest index so that any real element wins a tie.
     static DPB_D Acc identity()
     {
@@ -186,6 +191,31 @@ struct SearchRed {
             }
             return r;
         }
+    }
+    // Accumulate N adjacent elements starting at index i0.  Only when the best of the
+    // group can beat the accumulator (rare once the scan has warmed up, and never for
+    // a mere tie) are the elements examined one by one.
+    template <int N> static DPB_D Acc step_vec(const Acc &a, const In (&v)[N], int64_t i0)
+    {
+        V x[N];
+        bool any_nan = false;
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            if constexpr (is_bool_v<TIn>) x[k] = v[k].v ? 1 : 0;
+            else x[k] = convert<V>(v[k]);
+            if constexpr (std::is_floating_point_v<V>) any_nan = any_nan || (x[k] != x[k]);
+        }
+        V m = x[0];
+#pragma unroll
+        for (int k = 1; k < N; ++k) m = IS_MAX ? (x[k] > m ? x[k] : m) : (x[k] < m ? x[k] : m);
+        const bool maybe = (IS_MAX ? (m > a.val) : (m < a.val)) || any_nan ||
+                           (a.idx == std::numeric_limits<int64_t>::max());
+        Acc r = a;
+        if (maybe) {
+#pragma unroll
+            for (int k = 0; k < N; ++k) r = step(r, v[k], i0 + k);
+        }
+        return r;
     }
     static DPB_D Acc combine(const Acc &a, const Acc &b) { return search_better<IS_MAX>(a, b) ? a : b; }
     static DPB_D Out finish(const Acc &a) { return a.idx; }

@@ -27,12 +27,23 @@ def _make_unary(name, op):
         check(lib.dpb_unary_ufunc(op, C.byref(ds), C.byref(dd), _stream(sycl_queue)))
         return _events(sycl_queue)
 
+    cache = {}
+
     def result_type(dtype):
+        try:
+            return cache[dtype]
+        except (KeyError, TypeError):
+            pass
         try:
             t = lib.dpb_unary_result_type(op, _lib.typenum_of(dtype))
         except TypeError:
             return None
-        return None if t < 0 else _lib.dtype_of(t)
+        res = None if t < 0 else _lib.dtype_of(t)
+        try:
+            cache[dtype] = res
+        except TypeError:
+            pass
+        return res
 
     call.__name__ = f"_{name}"
     result_type.__name__ = f"_{name}_result_type"
@@ -48,12 +59,23 @@ def _make_binary(name, op):
         check(lib.dpb_binary_ufunc(op, C.byref(d1), C.byref(d2), C.byref(dd), _stream(sycl_queue)))
         return _events(sycl_queue)
 
+    cache = {}
+
     def result_type(dtype1, dtype2):
+        try:
+            return cache[(dtype1, dtype2)]
+        except (KeyError, TypeError):
+            pass
         try:
             t = lib.dpb_binary_result_type(op, _lib.typenum_of(dtype1), _lib.typenum_of(dtype2))
         except TypeError:
             return None
-        return None if t < 0 else _lib.dtype_of(t)
+        res = None if t < 0 else _lib.dtype_of(t)
+        try:
+            cache[(dtype1, dtype2)] = res
+        except TypeError:
+            pass
+        return res
 
     def inplace(lhs, rhs, sycl_queue, depends=()):
         _check_queue(sycl_queue, lhs, rhs)

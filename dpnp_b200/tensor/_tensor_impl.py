@@ -82,19 +82,17 @@ def _zeros_usm_ndarray(dst, sycl_queue, depends=()):
 
 
 def _array_overlap(a, b) -> bool:
-    da, ka = a._descriptor()
-    db, kb = b._descriptor()
-    out = C.c_int()
-    check(lib.dpb_array_overlap(C.byref(da), C.byref(db), C.byref(out)))
-    return bool(out.value)
+    """True if the byte ranges spanned by the two arrays intersect (the interval test of
+    include/utils/memory_overlap.hpp:52-107; dpb_array_overlap is the native form)."""
+    ea, eb = a._byte_extent(), b._byte_extent()
+    if ea is None or eb is None:
+        return False
+    return ea[0] < eb[1] and eb[0] < ea[1]
 
 
 def _same_logical_tensors(a, b) -> bool:
-    da, ka = a._descriptor()
-    db, kb = b._descriptor()
-    out = C.c_int()
-    check(lib.dpb_same_logical_tensors(C.byref(da), C.byref(db), C.byref(out)))
-    return bool(out.value)
+    """Same pointer, type, shape and strides (memory_overlap.hpp:109-151)."""
+    return (a._ptr == b._ptr and a.dtype == b.dtype and a.shape == b.shape and a.strides == b.strides)
 
 
 def _contract_iter(shape, strides):

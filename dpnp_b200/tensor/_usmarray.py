@@ -211,7 +211,10 @@ class usm_ndarray:
                                  bool(self._flags & FLAG_W), self._usm_type)
 
     def _descriptor(self):
-        """(dpb_array, keepalive) for the C ABI."""
+        """(dpb_array, keepalive) for the C ABI; built once per array object."""
+        cached = getattr(self, "_desc_cache", None)
+        if cached is not None:
+            return cached
         nd = len(self._shape)
         sh = (C.c_int64 * max(nd, 1))(*self._shape)
         st = (C.c_int64 * max(nd, 1))(*self._strides)
@@ -223,7 +226,29 @@ class usm_ndarray:
         d.device = self._queue.device
         d.shape = C.cast(sh, C.POINTER(C.c_int64))
         d.strides = C.cast(st, C.POINTER(C.c_int64))
-        return d, (sh, st)
+        self._desc_cache = (d, (sh, st))
+        return self._desc_cache
+
+    def _byte_extent(self):
+        """Half-open range of byte addresses the array can touch (None when empty)."""
+        ext = getattr(self, "_extent_cache", 0)
+        if ext != 0:
+            return ext
+        lo = hi = 0
+        empty = False
+        for sh, st in zip(self._shape, self._strides):
+            if sh == 0:
+                empty = True
+                break
+            span = st * (sh - 1)
+            if span < 0:
+                lo += span
+            else:
+                hi += span
+        item = self._dtype.itemsize
+        ext = None if empty else (self._ptr + lo * item, self._ptr + (hi + 1) * item)
+        self._extent_cache = ext
+        return ext
 
     # ----------------------------------------------------------- attributes
     @property
@@ -236,6 +261,8 @@ class usm_ndarray:
 
         r = reshape(self, new_shape, copy=False)
         self._shape, self._strides, self._flags = r._shape, r._strides, r._flags
+        self._desc_cache = None
+        self._extent_cache = 0
 
     @property
     def strides(self):

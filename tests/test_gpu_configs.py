@@ -111,7 +111,7 @@ def test_c4_transposed_broadcast_multiply():
     A = dp.random.uniform(-2, 2, (1024, 4096, 64), dtype="f4")
     B = dp.random.uniform(-2, 2, (64, 1, 4096), dtype="f4")
     out = dp.multiply(A.transpose(2, 0, 1), B)
-    assert _lib.last_kernel() in ("ew_transpose", "ew_transpose_tma")
+    assert _lib.last_kernel().startswith("ew_transpose")
     ref = dp.multiply(dp.copy(A.transpose(2, 0, 1), order="C"), B)
     assert bool(dp.all(out == ref))
     sl = out[5, 100:102, :].asnumpy()

@@ -179,7 +179,7 @@ def test_strided_broadcast_and_transposed_operands():
     a = rand(rng, "f4", (33, 70, 64))
     b = rand(rng, "f4", (64, 1, 70))
     got = dp.multiply(dev(a).transpose(2, 0, 1), dev(b))
-    assert _lib.last_kernel() == "ew_transpose"
+    assert _lib.last_kernel().startswith("ew_transpose")
     assert got.flags.c_contiguous and got.shape == (64, 33, 70)
     np.testing.assert_array_equal(got.asnumpy(), a.transpose(2, 0, 1) * b)
     m = rand(rng, "f8", (257, 130))
