@@ -573,7 +573,7 @@ int dpb_full_array(const dpb_array *dst, const void *scalar_bits, void *stream)
 #define DPB_FILL_CASE(B)                          \
     case B: {                                     \
         FillF<B> f;                               \
-        std::memcpy(f.v.b, scalar_bits, B);       \
+        std::memcpy(&f.v, scalar_bits, B);       \
         return launch_ew(f, plan, pin, pout, s);  \
     }
     switch (type_size(dst->typenum)) {

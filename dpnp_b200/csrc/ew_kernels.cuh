@@ -22,6 +22,8 @@
 // copy/cast kernels (include/kernels/copy_and_cast.hpp:90-389).
 #pragma once
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ew_plan.h"
 
@@ -60,17 +62,23 @@ template <class F> constexpr int ew_vec_width()
 }
 
 // ------------------------------------------------------------- contiguous
-// Tile = 256 threads x VEC elements x UNROLL vectors; blocks walk the tiles
-// with a grid stride; the ragged end is handled element-wise by one block.
-template <class F, int VEC, int UNROLL>
+// Tile = 256 threads x VEC elements x UNROLL vectors, one tile per block (the
+// kernel keeps a stride loop so a capped grid still covers any size); the ragged
+// end is handled element-wise by one block.  BMASK names, at compile time, the
+// inputs that are a single broadcast element: they cost one register instead of
+// a stream, which leaves room for a deeper unroll of the remaining stream.
+template <class F, int VEC, int UNROLL, unsigned BMASK>
 __global__ void __launch_bounds__(kEwThreads)
-    ew_contig_vec_kernel(F f, EwPtrs<F> p, int64_t n, unsigned bcast)
+    ew_contig_vec_kernel(F f, EwPtrs<F> p, int64_t n)
 {
     using In0 = typename F::In0;
     using In1 = typename F::In1;
     using In2 = typename F::In2;
     using Out = typename F::Out;
     constexpr int64_t TILE = int64_t(kEwThreads) * VEC * UNROLL;
+    constexpr bool S0 = F::NIN >= 1 && !(BMASK & 1u);  // input k streams from memory
+    constexpr bool S1 = F::NIN >= 2 && !(BMASK & 2u);
+    constexpr bool S2 = F::NIN >= 3 && !(BMASK & 4u);
     const In0 *a = static_cast<const In0 *>(p.in[0]);
     const In1 *b = static_cast<const In1 *>(p.in[1]);
     const In2 *c = static_cast<const In2 *>(p.in[2]);
@@ -79,22 +87,22 @@ __global__ void __launch_bounds__(kEwThreads)
     In0 sa{};
     In1 sb{};
     In2 sc{};
-    if constexpr (F::NIN >= 1) { if (bcast & 1u) sa = a[0]; }
-    if constexpr (F::NIN >= 2) { if (bcast & 2u) sb = b[0]; }
-    if constexpr (F::NIN >= 3) { if (bcast & 4u) sc = c[0]; }
+    if constexpr (F::NIN >= 1 && !S0) sa = a[0];
+    if constexpr (F::NIN >= 2 && !S1) sb = b[0];
+    if constexpr (F::NIN >= 3 && !S2) sc = c[0];
 
     const int64_t ntiles = n / TILE;
     for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
         const int64_t base = t * TILE + int64_t(threadIdx.x) * VEC;
-        vec_t<In0, VEC> va[UNROLL];
-        vec_t<In1, VEC> vb[UNROLL];
-        vec_t<In2, VEC> vc[UNROLL];
+        vec_t<In0, VEC> va[S0 ? UNROLL : 1];
+        vec_t<In1, VEC> vb[S1 ? UNROLL : 1];
+        vec_t<In2, VEC> vc[S2 ? UNROLL : 1];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int64_t i = base + int64_t(u) * kEwThreads * VEC;
-            if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) va[u] = load_vec<vec_t<In0, VEC>>(a + i); }
-            if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) vb[u] = load_vec<vec_t<In1, VEC>>(b + i); }
-            if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) vc[u] = load_vec<vec_t<In2, VEC>>(c + i); }
+            if constexpr (S0) va[u] = load_vec<vec_t<In0, VEC>>(a + i);
+            if constexpr (S1) vb[u] = load_vec<vec_t<In1, VEC>>(b + i);
+            if constexpr (S2) vc[u] = load_vec<vec_t<In2, VEC>>(c + i);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -105,9 +113,9 @@ __global__ void __launch_bounds__(kEwThreads)
                 In0 x = sa;
                 In1 y = sb;
                 In2 z = sc;
-                if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) x = va[u].v[k]; }
-                if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) y = vb[u].v[k]; }
-                if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) z = vc[u].v[k]; }
+                if constexpr (S0) x = va[u].v[k];
+                if constexpr (S1) y = vb[u].v[k];
+                if constexpr (S2) z = vc[u].v[k];
                 r.v[k] = ew_apply(f, x, y, z);
             }
             store_vec(o + i, r);
@@ -118,9 +126,9 @@ __global__ void __launch_bounds__(kEwThreads)
             In0 x = sa;
             In1 y = sb;
             In2 z = sc;
-            if constexpr (F::NIN >= 1) { if (!(bcast & 1u)) x = a[i]; }
-            if constexpr (F::NIN >= 2) { if (!(bcast & 2u)) y = b[i]; }
-            if constexpr (F::NIN >= 3) { if (!(bcast & 4u)) z = c[i]; }
+            if constexpr (S0) x = a[i];
+            if constexpr (S1) y = b[i];
+            if constexpr (S2) z = c[i];
             o[i] = ew_apply(f, x, y, z);
         }
     }
@@ -326,149 +334,125 @@ struct TileDivs {
     FastDiv32 per_row;    // tiles_q
 };
 
-template <class F>
-DPB_D void transpose_tile_origin(const StridedMeta<F::NIN + 1> &batch, const TileDivs &td, uint32_t w, int T,
-                                 int64_t &p0, int64_t &q0, int64_t (&off)[F::NIN + 1])
-{
-    constexpr int NARR = F::NIN + 1;
-    uint32_t bi, tw, tp, tq;
-    td.per_batch.divmod(w, bi, tw);
-    td.per_row.divmod(tw, tp, tq);
-    p0 = int64_t(tp) * T;
-    q0 = int64_t(tq) * T;
-#pragma unroll
-    for (int k = 0; k < NARR; ++k) off[k] = 0;
-    uint32_t rem = bi;
-    for (int d = batch.nd - 1; d >= 0; --d) {
-        uint32_t q, r;
-        batch.div[d].divmod(rem, q, r);
-        rem = q;
-#pragma unroll
-        for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * batch.strides[k][d];
-    }
-}
-
-// A block works through `tiles_per_block` consecutive tiles; the 16-byte loads
-// of the next tile's staged inputs are issued before the current tile is
-// combined and stored, so global loads stay in flight across the barriers.
-template <class F, int VEC>
-__global__ void __launch_bounds__(kEwThreads)
+// The kernel is instantiated per access pattern (STAGED / VECQ are compile-time
+// bit masks over the inputs) so that the tile loop carries no run-time mode
+// tests, and every per-thread address part that does not change from tile to
+// tile is computed once before the loop: per tile a thread adds one 64-bit tile
+// base to its precomputed offsets.  Interior tiles take a path without bounds
+// tests.
+template <class F, int VEC, unsigned STAGED, unsigned VECQ>
+__global__ void __launch_bounds__(kEwThreads, 4)
     ew_transpose_vec_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> batch, int64_t np, int64_t nq,
-                            TransposeStrides st, unsigned staged, unsigned vecq, TileDivs td,
-                            uint32_t nwork, int tiles_per_block)
+                            TransposeStrides st, TileDivs td, uint32_t nwork, int tiles_per_block)
 {
     using In0 = typename F::In0;
     using In1 = typename F::In1;
-    using In2 = typename F::In2;
     using Out = typename F::Out;
     constexpr int NARR = F::NIN + 1;
     constexpr int T = 16 * VEC;
-    __shared__ In0 s0[F::NIN >= 1 ? T : 1][T + 1];
-    __shared__ In1 s1[F::NIN >= 2 ? T : 1][T + 1];
+    constexpr bool ST0 = (STAGED & 1u) != 0, ST1 = (STAGED & 2u) != 0;
+    constexpr bool VQ0 = (VECQ & 1u) != 0, VQ1 = (VECQ & 2u) != 0;
+    static_assert(F::NIN == 1 || F::NIN == 2, "one or two inputs");
+    __shared__ In0 s0[ST0 ? T : 1][T + 1];
+    __shared__ In1 s1[ST1 ? T : 1][T + 1];
 
     const int lane16 = threadIdx.x & 15;  // vector index inside a tile row
     const int row16 = threadIdx.x >> 4;   // 0..15
+    // per-thread offsets relative to the tile origin, for pass r (rows row16 + 16 r)
+    int64_t ld0[VEC], ld1[VEC], in0[VEC], in1[VEC], so[VEC];
+#pragma unroll
+    for (int r = 0; r < VEC; ++r) {
+        const int64_t row = row16 + 16 * r;
+        ld0[r] = lane16 * VEC + row * st.sq[0];             // staged load: vector along P, row along Q
+        ld1[r] = lane16 * VEC + row * st.sq[1];
+        in0[r] = row * st.sp[0] + int64_t(lane16 * VEC) * (VQ0 ? 1 : st.sq[0]);  // read along Q, row along P
+        in1[r] = row * st.sp[1] + int64_t(lane16 * VEC) * (VQ1 ? 1 : st.sq[1]);
+        so[r] = row * st.spo + lane16 * VEC;
+    }
     const uint32_t w_begin = blockIdx.x * static_cast<uint32_t>(tiles_per_block);
     uint32_t w_end = w_begin + static_cast<uint32_t>(tiles_per_block);
     if (w_end > nwork || w_end < w_begin) w_end = nwork;
 
-    vec_t<In0, VEC> ra[VEC];
-    vec_t<In1, VEC> rb[VEC];
-
-    // issue the staged loads of tile w into registers
-    auto prefetch = [&](uint32_t w) {
-        int64_t p0, q0, off[NARR];
-        transpose_tile_origin<F>(batch, td, w, T, p0, q0, off);
-        const int64_t pp = p0 + lane16 * VEC;
+    for (uint32_t w = w_begin; w < w_end; ++w) {
+        uint32_t bi, tw, tp, tq;
+        td.per_batch.divmod(w, bi, tw);
+        td.per_row.divmod(tw, tp, tq);
+        const int64_t p0 = int64_t(tp) * T, q0 = int64_t(tq) * T;
+        int64_t off[NARR];
 #pragma unroll
-        for (int r = 0; r < VEC; ++r) {
-            const int64_t qq = q0 + row16 + 16 * r;
-            if (pp < np && qq < nq) {
-                if constexpr (F::NIN >= 1) {
-                    if (staged & 1u)
-                        ra[r] = load_vec<vec_t<In0, VEC>>(static_cast<const In0 *>(p.in[0]) + off[0] + pp +
-                                                          qq * st.sq[0]);
-                }
-                if constexpr (F::NIN >= 2) {
-                    if (staged & 2u)
-                        rb[r] = load_vec<vec_t<In1, VEC>>(static_cast<const In1 *>(p.in[1]) + off[1] + pp +
-                                                          qq * st.sq[1]);
-                }
+        for (int k = 0; k < NARR; ++k) off[k] = 0;
+        {
+            uint32_t rem = bi;
+            for (int d = batch.nd - 1; d >= 0; --d) {
+                uint32_t q, r;
+                batch.div[d].divmod(rem, q, r);
+                rem = q;
+#pragma unroll
+                for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * batch.strides[k][d];
             }
         }
-    };
+        const In0 *a = static_cast<const In0 *>(p.in[0]) + off[0];
+        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
+        Out *o = static_cast<Out *>(p.out) + off[NARR - 1] + p0 * st.spo + q0;
+        const In0 *a_st = a + p0 + q0 * st.sq[0];              // staged view of the tile
+        const In1 *b_st = b + p0 + q0 * st.sq[1];
+        const In0 *a_in = a + p0 * st.sp[0] + q0 * st.sq[0];   // direct view of the tile
+        const In1 *b_in = b + p0 * st.sp[1] + q0 * st.sq[1];
+        const bool full = (p0 + T <= np) && (q0 + T <= nq);
 
-    if (w_begin < w_end) prefetch(w_begin);
-    for (uint32_t w = w_begin; w < w_end; ++w) {
-        // registers -> transposed tile
+        // stage: 16-byte loads along P, scattered into the transposed tile
 #pragma unroll
         for (int r = 0; r < VEC; ++r) {
             const int qi = row16 + 16 * r;
+            if (full || (p0 + lane16 * VEC < np && q0 + qi < nq)) {
+                if constexpr (ST0) {
+                    const vec_t<In0, VEC> v = load_vec<vec_t<In0, VEC>>(a_st + ld0[r]);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-                if constexpr (F::NIN >= 1) { if (staged & 1u) s0[lane16 * VEC + e][qi] = ra[r].v[e]; }
-                if constexpr (F::NIN >= 2) { if (staged & 2u) s1[lane16 * VEC + e][qi] = rb[r].v[e]; }
+                    for (int e = 0; e < VEC; ++e) s0[lane16 * VEC + e][qi] = v.v[e];
+                }
+                if constexpr (ST1) {
+                    const vec_t<In1, VEC> v = load_vec<vec_t<In1, VEC>>(b_st + ld1[r]);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) s1[lane16 * VEC + e][qi] = v.v[e];
+                }
             }
         }
         __syncthreads();
-        if (w + 1 < w_end) prefetch(w + 1);
-
-        int64_t p0, q0, off[NARR];
-        transpose_tile_origin<F>(batch, td, w, T, p0, q0, off);
-        const In0 *a = static_cast<const In0 *>(p.in[0]) + (F::NIN >= 1 ? off[0] : 0);
-        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
-        const In2 *c = static_cast<const In2 *>(p.in[2]) + (F::NIN >= 3 ? off[2] : 0);
-        Out *o = static_cast<Out *>(p.out) + off[NARR - 1];
-        const int64_t qq = q0 + lane16 * VEC;
+        // combine: 16-byte accesses along Q
 #pragma unroll
         for (int r = 0; r < VEC; ++r) {
             const int pi = row16 + 16 * r;
-            const int64_t pp = p0 + pi;
-            if (pp < np && qq < nq) {
+            if (full || (p0 + pi < np && q0 + lane16 * VEC < nq)) {
                 vec_t<In0, VEC> x;
                 vec_t<In1, VEC> y;
-                vec_t<In2, VEC> z;
-                if constexpr (F::NIN >= 1) {
-                    if (staged & 1u) {
+                if constexpr (ST0) {
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) x.v[e] = s0[pi][lane16 * VEC + e];
-                    }
-                    else if (vecq & 1u) x = load_vec<vec_t<In0, VEC>>(a + pp * st.sp[0] + qq);
-                    else {
+                    for (int e = 0; e < VEC; ++e) x.v[e] = s0[pi][lane16 * VEC + e];
+                }
+                else if constexpr (VQ0) x = load_vec<vec_t<In0, VEC>>(a_in + in0[r]);
+                else {
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) x.v[e] = a[pp * st.sp[0] + (qq + e) * st.sq[0]];
-                    }
+                    for (int e = 0; e < VEC; ++e) x.v[e] = a_in[in0[r] + e * st.sq[0]];
                 }
                 if constexpr (F::NIN >= 2) {
-                    if (staged & 2u) {
+                    if constexpr (ST1) {
 #pragma unroll
                         for (int e = 0; e < VEC; ++e) y.v[e] = s1[pi][lane16 * VEC + e];
                     }
-                    else if (vecq & 2u) y = load_vec<vec_t<In1, VEC>>(b + pp * st.sp[1] + qq);
+                    else if constexpr (VQ1) y = load_vec<vec_t<In1, VEC>>(b_in + in1[r]);
                     else {
 #pragma unroll
-                        for (int e = 0; e < VEC; ++e) y.v[e] = b[pp * st.sp[1] + (qq + e) * st.sq[1]];
-                    }
-                }
-                if constexpr (F::NIN >= 3) {
-                    if (vecq & 4u) z = load_vec<vec_t<In2, VEC>>(c + pp * st.sp[2] + qq);
-                    else {
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) z.v[e] = c[pp * st.sp[2] + (qq + e) * st.sq[2]];
+                        for (int e = 0; e < VEC; ++e) y.v[e] = b_in[in1[r] + e * st.sq[1]];
                     }
                 }
                 vec_t<Out, VEC> res;
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
-                    In0 xe{};
                     In1 ye{};
-                    In2 ze{};
-                    if constexpr (F::NIN >= 1) xe = x.v[e];
                     if constexpr (F::NIN >= 2) ye = y.v[e];
-                    if constexpr (F::NIN >= 3) ze = z.v[e];
-                    res.v[e] = ew_apply(f, xe, ye, ze);
+                    res.v[e] = ew_apply(f, x.v[e], ye, char(0));
                 }
-                store_vec(o + pp * st.spo + qq, res);
+                store_vec(o + so[r], res);
             }
         }
         __syncthreads();
@@ -583,21 +567,35 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         bool aligned = is_aligned(out, sizeof(Out) * VEC);
         for (int k = 0; k < NIN; ++k)
             if (!(plan.bcast_mask & (1u << k))) aligned = aligned && is_aligned(in[k], in_sizes[k] * VEC);
-        if (aligned && VEC > 1) {
-            constexpr int UNROLL = 4;
-            const int64_t tiles = plan.n / (int64_t(kEwThreads) * VEC * UNROLL);
-            ew_contig_vec_kernel<F, VEC, UNROLL>
-                <<<ew_flat_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
-            note_kernel("ew_contig_vec");
+        const unsigned m = plan.bcast_mask;
+        // the vector kernel is instantiated for the broadcast patterns that occur in practice;
+        // anything else (unaligned pointers, odd patterns) takes the rows kernel below
+#define DPB_CONTIG_LAUNCH(U, MASK)                                                                  \
+    {                                                                                               \
+        const int64_t tiles = plan.n / (int64_t(kEwThreads) * VEC * (U));                           \
+        ew_contig_vec_kernel<F, VEC, U, MASK><<<ew_flat_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n); \
+        note_kernel("ew_contig_vec");                                                               \
+        return check_launch("ew_contig_vec");                                                       \
+    }
+        if (aligned) {
+            if constexpr (NIN == 0) DPB_CONTIG_LAUNCH(8, 0u)
+            if constexpr (NIN == 1) {
+                if (m == 0) DPB_CONTIG_LAUNCH(8, 0u)
+            }
+            if constexpr (NIN == 2) {
+                if (m == 0) DPB_CONTIG_LAUNCH(4, 0u)
+                if (m == 1) DPB_CONTIG_LAUNCH(8, 1u)
+                if (m == 2) DPB_CONTIG_LAUNCH(8, 2u)
+            }
+            if constexpr (NIN == 3) {
+                if (m == 0) DPB_CONTIG_LAUNCH(4, 0u)
+                if (m == 2) DPB_CONTIG_LAUNCH(4, 2u)
+                if (m == 4) DPB_CONTIG_LAUNCH(4, 4u)
+                if (m == 6) DPB_CONTIG_LAUNCH(8, 6u)
+            }
         }
-        else {
-            constexpr int UNROLL = 4;
-            const int64_t tiles = plan.n / (int64_t(kEwThreads) * UNROLL);
-            ew_contig_vec_kernel<F, 1, UNROLL>
-                <<<ew_flat_grid(tiles), kEwThreads, 0, stream>>>(f, p, plan.n, plan.bcast_mask);
-            note_kernel("ew_contig_scalar");
-        }
-        return check_launch("ew_contig");
+#undef DPB_CONTIG_LAUNCH
+        // fall through: a contiguous plan is a rows plan with no outer dimensions
     }
     case EW_ROWS: {
         const int last = plan.nd - 1;
@@ -655,16 +653,17 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
             StridedMeta<NARR> batch;
             fill_meta(batch, plan, dims, nb, arr_index);
             const int64_t np = plan.shape[pd], nq = plan.shape[q];
-            // vector form: one element size (4 or 8 bytes) everywhere, at most the first two
-            // inputs staged, every vector access 16-byte aligned
-            if constexpr (NIN >= 1 && (sizeof(Out) == 4 || sizeof(Out) == 8) &&
-                          (NIN < 1 || sizeof(typename F::In0) == sizeof(Out)) &&
-                          (NIN < 2 || sizeof(typename F::In1) == sizeof(Out)) &&
-                          (NIN < 3 || sizeof(typename F::In2) == sizeof(Out))) {
+            // vector form: one or two inputs of one element size (4 or 8 bytes), every vector
+            // access 16-byte aligned; instantiated per access pattern
+            if constexpr ((NIN == 1 || NIN == 2) && (sizeof(Out) == 4 || sizeof(Out) == 8) &&
+                          sizeof(typename F::In0) == sizeof(Out) &&
+                          (NIN < 2 || sizeof(typename F::In1) == sizeof(Out))) {
                 constexpr int TV = 16 / static_cast<int>(sizeof(Out));
-                bool ok = !(plan.staged_mask & 4u) && np % TV == 0 && nq % TV == 0 && is_aligned(out, 16) &&
-                          plan.strides[NARR - 1][pd] % TV == 0 &&
-                          nbatch * ceil_div(np, 16 * TV) * ceil_div(nq, 16 * TV) < (int64_t(1) << 31);
+                constexpr int T = 16 * TV;
+                const int64_t tp = ceil_div(np, T), tq = ceil_div(nq, T);
+                const int64_t nw = nbatch * tp * tq;
+                bool ok = np % TV == 0 && nq % TV == 0 && is_aligned(out, 16) &&
+                          plan.strides[NARR - 1][pd] % TV == 0 && nw < (int64_t(1) << 31);
                 for (int i = 0; i < nb && ok; ++i) ok = plan.strides[NARR - 1][dims[i]] % TV == 0;
                 unsigned vecq = 0;
                 for (int k = 0; k < NIN && ok; ++k) {
@@ -678,27 +677,37 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
                     }
                 }
                 if (ok) {
-                    constexpr int T = 16 * TV;
                     TransposeStrides ts;
                     for (int k = 0; k < 3; ++k) {
                         ts.sp[k] = k < NIN ? plan.strides[k][pd] : 0;
                         ts.sq[k] = k < NIN ? plan.strides[k][q] : 0;
                     }
                     ts.spo = plan.strides[NARR - 1][pd];
-                    const int64_t tp = ceil_div(np, T), tq = ceil_div(nq, T);
-                    const int64_t nw = nbatch * tp * tq;
-                    // consecutive tiles per block (so loads can run ahead), many blocks per SM
-                    const int tpb = nw >= int64_t(device_props().sm_count) * 64 ? 8 : 1;
-                    const int64_t nblocks = ceil_div(nw, tpb);
-                    if (nblocks > 0x7fffffffLL)
-                        return set_error(DPB_ERR_RUNTIME, "iteration space too large for the tiled kernel");
+                    const int tpb = nw >= int64_t(device_props().sm_count) * 64 ? 4 : 1;
+                    const unsigned nblocks = static_cast<unsigned>(ceil_div(nw, tpb));
                     TileDivs td;
                     td.per_batch = FastDiv32(static_cast<uint32_t>(tp * tq));
                     td.per_row = FastDiv32(static_cast<uint32_t>(tq));
-                    ew_transpose_vec_kernel<F, TV><<<static_cast<unsigned>(nblocks), kEwThreads, 0, stream>>>(
-                        f, p, batch, np, nq, ts, plan.staged_mask, vecq, td, static_cast<uint32_t>(nw), tpb);
-                    note_kernel("ew_transpose_vec");
-                    return check_launch("ew_transpose_vec");
+                    const uint32_t nw32 = static_cast<uint32_t>(nw);
+                    const unsigned sm = plan.staged_mask;
+#define DPB_TR_LAUNCH(S, V)                                                                          \
+    {                                                                                                \
+        ew_transpose_vec_kernel<F, TV, S, V><<<nblocks, kEwThreads, 0, stream>>>(f, p, batch, np, nq, ts, \
+                                                                                 td, nw32, tpb);      \
+        note_kernel("ew_transpose_vec");                                                             \
+        return check_launch("ew_transpose_vec");                                                     \
+    }
+                    if constexpr (NIN == 1) {
+                        if (sm == 1u) DPB_TR_LAUNCH(1u, 0u)
+                    }
+                    else {
+                        if (sm == 1u && vecq == 2u) DPB_TR_LAUNCH(1u, 2u)
+                        if (sm == 2u && vecq == 1u) DPB_TR_LAUNCH(2u, 1u)
+                        if (sm == 3u) DPB_TR_LAUNCH(3u, 0u)
+                        if (sm == 1u && vecq == 0u) DPB_TR_LAUNCH(1u, 0u)
+                        if (sm == 2u && vecq == 0u) DPB_TR_LAUNCH(2u, 0u)
+                    }
+#undef DPB_TR_LAUNCH
                 }
             }
             const int64_t tiles_p = ceil_div(np, kTile), tiles_q = ceil_div(nq, kTile);

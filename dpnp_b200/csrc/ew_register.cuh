@@ -66,9 +66,15 @@ template <template <class, class> class Op, class A, class B> struct BinaryF {
     DPB_D Out operator()(In0 x, In1 y) const { return Op<A, B>::apply(x, y); }
 };
 
-// opaque value of a given size, used where the operation only moves bits
+// opaque value of a given size, used where the operation only moves bits; the payload is
+// a machine word (or two) so that copies compile to register moves
+template <int BYTES> struct blob_word { using type = unsigned char; static constexpr int N = BYTES; };
+template <> struct blob_word<2> { using type = uint16_t; static constexpr int N = 1; };
+template <> struct blob_word<4> { using type = uint32_t; static constexpr int N = 1; };
+template <> struct blob_word<8> { using type = uint64_t; static constexpr int N = 1; };
+template <> struct blob_word<16> { using type = uint64_t; static constexpr int N = 2; };
 template <int BYTES> struct alignas(BYTES) blob_t {
-    unsigned char b[BYTES];
+    typename blob_word<BYTES>::type w[blob_word<BYTES>::N];
 };
 
 template <class C, int BYTES> struct WhereF {

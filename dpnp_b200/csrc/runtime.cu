@@ -71,6 +71,7 @@ const DeviceProps &device_props()
 static std::atomic<int64_t> g_ctas_per_sm{8};
 int64_t tuning_ctas_per_sm() { return g_ctas_per_sm.load(std::memory_order_relaxed); }
 
+
 // ------------------------------------------------------------------- pool
 struct PoolState {
     std::atomic<bool> configured{false};
