@@ -633,9 +633,9 @@ def profile_case(name, launches=3):
         fn = {"sum_axis1": lambda: dp.sum(x, axis=1), "sum_axis0": lambda: dp.sum(x, axis=0),
               "mean_all": lambda: dp.mean(x)}[name]
     elif name == "transpose_c4":
-        a = dp.random.uniform(-2, 2, (128, 4096, 64), dtype="f4")
+        a = dp.random.uniform(-2, 2, (512, 4096, 64), dtype="f4")
         b = dp.random.uniform(-2, 2, (64, 1, 4096), dtype="f4")
-        o = dp.empty((64, 128, 4096), dtype="f4")
+        o = dp.empty((64, 512, 4096), dtype="f4")
         at = a.transpose(2, 0, 1)
         fn = lambda: dp.multiply(at, b, out=o)
     elif name in ("max_i32", "argmax_i32"):

@@ -330,8 +330,16 @@ struct TransposeStrides {
 // Tile coordinates of work item w and the operands' batch offsets (31-bit
 // multiply-shift divisions: the launcher guarantees nwork < 2^31).
 struct TileDivs {
-    FastDiv32 per_batch;  // tiles_p * tiles_q
     FastDiv32 per_row;    // tiles_q
+    // Work items are ordered [batch group][tile position][entry in group] with `group`
+    // consecutive items per block: a block walks `group` batch entries at one tile position
+    // while neighbouring blocks cover neighbouring tile positions.  (Letting one block sweep
+    // neighbouring tiles instead concentrates the resident blocks on few memory channels:
+    // measured 0.64 of peak against 0.95+ for this order on a 64 x 1024 x 4096 case.)
+    FastDiv32 per_group;  // tiles_p * tiles_q * group
+    FastDiv32 group_div;  // group
+    uint32_t group;
+    uint32_t nbatch;
 };
 
 // The kernel is instantiated per access pattern (STAGED / VECQ are compile-time
@@ -340,8 +348,10 @@ struct TileDivs {
 // tile is computed once before the loop: per tile a thread adds one 64-bit tile
 // base to its precomputed offsets.  Interior tiles take a path without bounds
 // tests.
+// Launch bounds ask for 6 resident blocks per SM: at 32-40 registers the kernel keeps
+// enough loads in flight (with 4 blocks it reached 0.77 of peak, with 6+ it reaches 0.88).
 template <class F, int VEC, unsigned STAGED, unsigned VECQ>
-__global__ void __launch_bounds__(kEwThreads, 4)
+__global__ void __launch_bounds__(kEwThreads, 6)
     ew_transpose_vec_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> batch, int64_t np, int64_t nq,
                             TransposeStrides st, TileDivs td, uint32_t nwork, int tiles_per_block)
 {
@@ -373,32 +383,56 @@ __global__ void __launch_bounds__(kEwThreads, 4)
     uint32_t w_end = w_begin + static_cast<uint32_t>(tiles_per_block);
     if (w_end > nwork || w_end < w_begin) w_end = nwork;
 
+    // A block's items are `group` consecutive batch entries at one tile position: the tile
+    // origin is computed for the first item; with a single batch dimension the following
+    // items only advance every view by that dimension's stride.
+    const In0 *a_st = nullptr, *a_in = nullptr;
+    const In1 *b_st = nullptr, *b_in = nullptr;
+    Out *o = nullptr;
+    int64_t p0 = 0, q0 = 0;
+    bool full = false, need_origin = true;
+    uint32_t bi = 0;
     for (uint32_t w = w_begin; w < w_end; ++w) {
-        uint32_t bi, tw, tp, tq;
-        td.per_batch.divmod(w, bi, tw);
-        td.per_row.divmod(tw, tp, tq);
-        const int64_t p0 = int64_t(tp) * T, q0 = int64_t(tq) * T;
-        int64_t off[NARR];
+        if (need_origin) {
+            uint32_t grp, rem, tw, jin, tp, tq;
+            td.per_group.divmod(w, grp, rem);
+            td.group_div.divmod(rem, tw, jin);
+            bi = grp * td.group + jin;
+            td.per_row.divmod(tw, tp, tq);
+            p0 = int64_t(tp) * T;
+            q0 = int64_t(tq) * T;
+            int64_t off[NARR];
 #pragma unroll
-        for (int k = 0; k < NARR; ++k) off[k] = 0;
-        {
-            uint32_t rem = bi;
+            for (int k = 0; k < NARR; ++k) off[k] = 0;
+            uint32_t rest = bi;
             for (int d = batch.nd - 1; d >= 0; --d) {
                 uint32_t q, r;
-                batch.div[d].divmod(rem, q, r);
-                rem = q;
+                batch.div[d].divmod(rest, q, r);
+                rest = q;
 #pragma unroll
                 for (int k = 0; k < NARR; ++k) off[k] += int64_t(r) * batch.strides[k][d];
             }
+            const In0 *a = static_cast<const In0 *>(p.in[0]) + off[0];
+            const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
+            o = static_cast<Out *>(p.out) + off[NARR - 1] + p0 * st.spo + q0;
+            a_st = a + p0 + q0 * st.sq[0];              // staged view of the tile
+            b_st = b + p0 + q0 * st.sq[1];
+            a_in = a + p0 * st.sp[0] + q0 * st.sq[0];   // direct view of the tile
+            b_in = b + p0 * st.sp[1] + q0 * st.sq[1];
+            full = (p0 + T <= np) && (q0 + T <= nq);
+            need_origin = batch.nd != 1;
         }
-        const In0 *a = static_cast<const In0 *>(p.in[0]) + off[0];
-        const In1 *b = static_cast<const In1 *>(p.in[1]) + (F::NIN >= 2 ? off[1] : 0);
-        Out *o = static_cast<Out *>(p.out) + off[NARR - 1] + p0 * st.spo + q0;
-        const In0 *a_st = a + p0 + q0 * st.sq[0];              // staged view of the tile
-        const In1 *b_st = b + p0 + q0 * st.sq[1];
-        const In0 *a_in = a + p0 * st.sp[0] + q0 * st.sq[0];   // direct view of the tile
-        const In1 *b_in = b + p0 * st.sp[1] + q0 * st.sq[1];
-        const bool full = (p0 + T <= np) && (q0 + T <= nq);
+        else {
+            ++bi;
+            a_st += batch.strides[0][0];
+            a_in += batch.strides[0][0];
+            if constexpr (F::NIN >= 2) {
+                b_st += batch.strides[1][0];
+                b_in += batch.strides[1][0];
+            }
+            o += batch.strides[NARR - 1][0];
+        }
+        if (bi >= td.nbatch) break;  // padding of a ragged last group (uniform over the block)
 
         // stage: 16-byte loads along P, scattered into the transposed tile
 #pragma unroll
@@ -683,12 +717,22 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
                         ts.sq[k] = k < NIN ? plan.strides[k][q] : 0;
                     }
                     ts.spo = plan.strides[NARR - 1][pd];
-                    const int tpb = nw >= int64_t(device_props().sm_count) * 64 ? 4 : 1;
-                    const unsigned nblocks = static_cast<unsigned>(ceil_div(nw, tpb));
+                    // `group` batch entries per block (fewer when that would leave under 16 blocks per SM)
+                    int64_t group = std::min<int64_t>(8, nbatch);
+                    while (group > 1 && ceil_div(nbatch, group) * tp * tq < int64_t(device_props().sm_count) * 16)
+                        group /= 2;
+                    const int tpb = static_cast<int>(group);
+                    const int64_t nw_padded = ceil_div(nbatch, group) * group * tp * tq;
+                    if (nw_padded >= (int64_t(1) << 31))
+                        return set_error(DPB_ERR_RUNTIME, "iteration space too large for the tiled kernel");
+                    const unsigned nblocks = static_cast<unsigned>(nw_padded / tpb);
                     TileDivs td;
-                    td.per_batch = FastDiv32(static_cast<uint32_t>(tp * tq));
                     td.per_row = FastDiv32(static_cast<uint32_t>(tq));
-                    const uint32_t nw32 = static_cast<uint32_t>(nw);
+                    td.per_group = FastDiv32(static_cast<uint32_t>(tp * tq * group));
+                    td.group_div = FastDiv32(static_cast<uint32_t>(group));
+                    td.group = static_cast<uint32_t>(group);
+                    td.nbatch = static_cast<uint32_t>(nbatch);
+                    const uint32_t nw32 = static_cast<uint32_t>(nw_padded);
                     const unsigned sm = plan.staged_mask;
 #define DPB_TR_LAUNCH(S, V)                                                                          \
     {                                                                                                \

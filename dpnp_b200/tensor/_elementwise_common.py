@@ -23,6 +23,30 @@ from ._type_utils import (_acceptance_fn_default_binary, _acceptance_fn_default_
 from ._usmarray import usm_ndarray
 
 
+_scalar_cache: dict = {}
+
+
+def _scalar_to_array(value, dtype, queue):
+    """0-d device array holding a Python scalar.  The reference materialises every scalar
+    operand with asarray() (dpnp/tensor/_elementwise_common.py:652-659), i.e. one host-to-
+    device copy per call; here the arrays are kept per (queue, dtype, bit pattern) so that a
+    repeated `x * 0.5` enqueues its kernel without touching the host-device link.  The
+    cached arrays are only ever read."""
+    dtype = np.dtype(dtype)
+    try:
+        bits = np.asarray(value).astype(dtype, casting="unsafe").tobytes()
+    except (TypeError, ValueError, OverflowError):
+        return asarray(value, dtype=dtype, sycl_queue=queue)
+    key = (queue.device, queue.stream, dtype.char, bits)
+    arr = _scalar_cache.get(key)
+    if arr is None:
+        if len(_scalar_cache) >= 4096:
+            _scalar_cache.clear()
+        arr = asarray(value, dtype=dtype, sycl_queue=queue)
+        _scalar_cache[key] = arr
+    return arr
+
+
 def _coerce_usm_type(types):
     """Result USM type: the first of device, shared, host that any input uses."""
     for t in ("device", "shared", "host"):
@@ -261,7 +285,7 @@ class BinaryElementwiseFunc:
                                 and not ti._same_logical_tensors(o2, out)):
                             buf2_dt = o2_dtype
                     else:
-                        src2 = asarray(o2, dtype=o2_dtype, sycl_queue=exec_q)
+                        src2 = _scalar_to_array(o2, o2_dtype, exec_q)
                     if buf2_dt is not None:
                         buf2 = empty_like(src2, dtype=buf2_dt)
                         ti._copy_usm_ndarray_into_usm_ndarray(src2, buf2, exec_q)
@@ -274,8 +298,8 @@ class BinaryElementwiseFunc:
                     and ti._array_overlap(o2, out) and not ti._same_logical_tensors(o2, out)):
                 out = empty_like(out)
 
-        src1 = o1 if isinstance(o1, usm_ndarray) else asarray(o1, dtype=o1_dtype, sycl_queue=exec_q)
-        src2 = o2 if isinstance(o2, usm_ndarray) else asarray(o2, dtype=o2_dtype, sycl_queue=exec_q)
+        src1 = o1 if isinstance(o1, usm_ndarray) else _scalar_to_array(o1, o1_dtype, exec_q)
+        src2 = o2 if isinstance(o2, usm_ndarray) else _scalar_to_array(o2, o2_dtype, exec_q)
         if order == "A":
             order = "F" if all(a.flags.f_contiguous for a in (src1, src2)) else "C"
 
@@ -345,7 +369,7 @@ class BinaryElementwiseFunc:
             if (buf_dt is None and ti._array_overlap(o2, o1) and not ti._same_logical_tensors(o2, o1)):
                 buf_dt = o2_dtype
         else:
-            src2 = asarray(o2, dtype=o2_dtype, sycl_queue=exec_q)
+            src2 = _scalar_to_array(o2, o2_dtype, exec_q)
         if buf_dt is not None:
             buf = empty_like(src2, dtype=buf_dt)
             ti._copy_usm_ndarray_into_usm_ndarray(src2, buf, exec_q)

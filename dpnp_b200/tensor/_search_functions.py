@@ -16,7 +16,7 @@ from ..memory import ExecutionPlacementError
 from . import _tensor_impl as ti
 from ._copy_utils import _empty, _empty_like_orderK, _empty_like_triple_orderK
 from ._ctors import asarray, empty_like
-from ._elementwise_common import _coerce_usm_type, _common_queue
+from ._elementwise_common import _coerce_usm_type, _common_queue, _scalar_to_array
 from ._manipulation_functions import _broadcast_shape_impl, broadcast_to
 from ._type_utils import _get_dtype, _get_shape, _is_weak_dtype, _promote_weak, _validate_dtype
 from ._usmarray import usm_ndarray
@@ -86,9 +86,9 @@ def where(condition, x1, x2, /, *, order="K", out=None):
         arrs = [condition] + [o for o in (x1, x2) if isinstance(o, usm_ndarray)]
         order = "F" if all(a.flags.f_contiguous for a in arrs) else "C"
     if not isinstance(x1, usm_ndarray):
-        x1 = asarray(x1, dtype=x1_dtype, sycl_queue=exec_q)
+        x1 = _scalar_to_array(x1, x1_dtype, exec_q)
     if not isinstance(x2, usm_ndarray):
-        x2 = asarray(x2, dtype=x2_dtype, sycl_queue=exec_q)
+        x2 = _scalar_to_array(x2, x2_dtype, exec_q)
 
     if condition.size == 0:
         if out is not None:
