@@ -169,6 +169,7 @@ def cpu_chain_throughput(n_sample, min_seconds=8.0, max_reps=6):
     """Options/s of the C restatement of the chain on all host cores (bounded sample)."""
     from oracle import dpnp_oracle as orc
 
+    cpu_threads()
     rng = np.random.default_rng(SEED)
     p, k, t = rng.uniform(10, 50, n_sample), rng.uniform(10, 50, n_sample), rng.uniform(1, 2, n_sample)
     orc.black_scholes_c(p[:1024], k[:1024], t[:1024], RATE, VOL, threads=True)  # warm up the thread pool
@@ -185,10 +186,19 @@ def cpu_chain_throughput(n_sample, min_seconds=8.0, max_reps=6):
 
 
 def cpu_threads():
+    """Use every core this process may run on, whatever OMP_NUM_THREADS the launcher exported;
+    returns the thread count the C port will actually use."""
     try:
-        return len(os.sched_getaffinity(0))
+        n = len(os.sched_getaffinity(0))
     except Exception:
-        return os.cpu_count() or 1
+        n = os.cpu_count() or 1
+    try:
+        from oracle import dpnp_oracle as orc
+
+        orc.core().orc_set_num_threads(int(n))
+        return int(orc.core().orc_max_threads())
+    except Exception:
+        return 1
 
 
 def run_reference_arm(args):
@@ -198,6 +208,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     n_sample = 1 << 26
+    threads = cpu_threads()
     # warm-up steps
     from oracle import dpnp_oracle as orc
 
@@ -211,7 +222,7 @@ def run_reference_arm(args):
     dt = time.perf_counter() - t0
     opt_per_s = n_sample * args.steps / dt
     value = opt_per_s * BYTES_PER_OPTION_CHAIN / 1e9
-    sample = f"all 2^26 options per step, {args.steps} steps, C chain with libm on {cpu_threads()} threads"
+    sample = f"all 2^26 options per step, {args.steps} steps, C chain with libm on {threads} threads"
     line = {
         "impl": "reference", "metric": "achieved algorithmic GB/s, Black-Scholes chain (552 B/option)",
         "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -219,7 +230,7 @@ def run_reference_arm(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": "black_scholes_f64_2^26_chain_26ufuncs_2copies", "options": N_OPTIONS,
                    "rate": RATE, "vol": VOL, "seed": SEED},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference not installable offline (DPC++/SYCL, dpctl, oneMKL absent): CPU port timed instead",
     }
@@ -256,7 +267,12 @@ def run_gpu_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
+    saved_stdout = None
     if world > 1:
+        # NCCL may print its version banner on stdout; keep stdout clean for the one JSON line
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         import torch
         import torch.distributed as dist
 
@@ -410,6 +426,10 @@ def run_gpu_arm(args):
         except Exception as exc:  # the checker is optional for the measurement itself
             cpu = {"value": None, "unit": "GB/s", "cores": cpu_threads(), "kind": "port", "sample": f"failed: {exc}"}
 
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     if rank == 0:
         line = {
             "metric": "achieved algorithmic GB/s, Black-Scholes chain (552 B/option)",
@@ -426,6 +446,7 @@ def run_gpu_arm(args):
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
+        os.dup2(2, 1)  # anything the teardown prints goes to stderr
         dist.barrier()
         dist.destroy_process_group()
 
@@ -443,6 +464,8 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     S = C.c_void_p(q.stream)
 
     def rec(name, nbytes, ms, kernel=None, note=None):
+        if os.environ.get("DPNP_B200_BENCH_VERBOSE"):
+            print(f"[rank {rank}] {name}: {ms:.3f} ms", file=sys.stderr, flush=True)
         gbs = nbytes / (ms * 1e-3) / 1e9
         r = {"op": name, "ms": ms, "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_peak": gbs / peak,
              "kernel": kernel or _lib.last_kernel()}

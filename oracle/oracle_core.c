@@ -18,6 +18,29 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Thread count of the multi-threaded variants (launchers such as torchrun export
+ * OMP_NUM_THREADS=1, which would silently turn the all-cores baseline into one core). */
+void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+int orc_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
 
 /* Element displacement of the i-th element (C order over `shape`) of an array
  * with the given strides: the computation of CIndexer_vector::get_displacement
