@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kEwThreads)
 // operand; `outer` describes the remaining dimensions.  A block is TX threads
 // along the row times TY rows; a work item is (row group, chunk of the row).
 template <class F, int VEC, int UNROLL>
-__global__ void __launch_bounds__(kEwThreads)
+__global__ void __launch_bounds__(kEwThreads, 5)
     ew_rows_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> outer, int64_t L, unsigned inner_bcast,
                    int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div)
 {

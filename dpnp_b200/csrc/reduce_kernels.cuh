@@ -132,7 +132,7 @@ template <class R> DPB_D void red_store(void *res, int64_t index, const typename
 template <class R, int VEC, int GROUP, int UNROLL>
 __global__ void __launch_bounds__(kRedThreads)
     reduce_inner_kernel(const typename R::In *arg, void *res, RedMeta iter, int64_t nrows, int64_t L,
-                        int64_t nsplit, int64_t chunk, bool final_pass)
+                        int64_t nsplit, int64_t chunk, bool final_pass, int64_t index_rows)
 {
     using In = typename R::In;
     using Acc = typename R::Acc;
@@ -156,12 +156,15 @@ __global__ void __launch_bounds__(kRedThreads)
             int64_t len = L - begin;
             if (len > chunk) len = chunk;
             const In *p = arg + o_src + begin;
+            // reduction index of the first element: rows that are slices of one result
+            // (index_rows of them per result, in order) continue each other's numbering
+            const int64_t ib = begin + (index_rows > 1 ? (row % index_rows) * L : 0);
             if constexpr (VEC > 1 && GROUP > 1) {
                 // peel up to the next 16-byte boundary
                 const uintptr_t addr = reinterpret_cast<uintptr_t>(p) / sizeof(In);
                 int64_t head = static_cast<int64_t>((VEC - (addr % VEC)) % VEC);
                 if (head > len) head = len;
-                if (t < head) acc = R::step(acc, p[t], begin + t);
+                if (t < head) acc = R::step(acc, p[t], ib + t);
                 const In *q = p + head;
                 const int64_t nvec = (len - head) / VEC;
                 if constexpr (R::kVectorStep) {
@@ -178,11 +181,11 @@ __global__ void __launch_bounds__(kRedThreads)
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u)
                             la[u] = R::template step_vec<VEC>(la[u], x[u].v,
-                                                               begin + head + (v + int64_t(u) * GROUP) * VEC);
+                                                               ib + head + (v + int64_t(u) * GROUP) * VEC);
                     }
                     for (; v < nvec; v += GROUP) {
                         vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(q + v * VEC);
-                        la[0] = R::template step_vec<VEC>(la[0], x.v, begin + head + v * VEC);
+                        la[0] = R::template step_vec<VEC>(la[0], x.v, ib + head + v * VEC);
                     }
 #pragma unroll
                     for (int u = 0; u < UNROLL; ++u) acc = R::combine(acc, la[u]);
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(kRedThreads)
                             x[u] = load_vec<vec_t<In, VEC>>(q + (v + int64_t(u) * GROUP) * VEC);
 #pragma unroll
                         for (int u = 0; u < UNROLL; ++u) {
-                            const int64_t e0 = begin + head + (v + int64_t(u) * GROUP) * VEC;
+                            const int64_t e0 = ib + head + (v + int64_t(u) * GROUP) * VEC;
 #pragma unroll
                             for (int k = 0; k < VEC; ++k)
                                 lanes[u % LU][k] = R::step(lanes[u % LU][k], x[u].v[k], e0 + k);
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(kRedThreads)
                     }
                     for (; v < nvec; v += GROUP) {
                         vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(q + v * VEC);
-                        const int64_t e0 = begin + head + v * VEC;
+                        const int64_t e0 = ib + head + v * VEC;
 #pragma unroll
                         for (int k = 0; k < VEC; ++k)
                             lanes[0][k] = R::step(lanes[0][k], x.v[k], e0 + k);
@@ -222,7 +225,7 @@ __global__ void __launch_bounds__(kRedThreads)
                         for (int k = 0; k < VEC; ++k) acc = R::combine(acc, lanes[u][k]);
                 }
                 const int64_t done = head + nvec * VEC;
-                if (done + t < len) acc = R::step(acc, p[done + t], begin + done + t);
+                if (done + t < len) acc = R::step(acc, p[done + t], ib + done + t);
             }
             else {
                 Acc lanes[UNROLL];
@@ -235,9 +238,9 @@ __global__ void __launch_bounds__(kRedThreads)
                     for (int u = 0; u < UNROLL; ++u) x[u] = p[e + int64_t(u) * GROUP];
 #pragma unroll
                     for (int u = 0; u < UNROLL; ++u)
-                        lanes[u] = R::step(lanes[u], x[u], begin + e + int64_t(u) * GROUP);
+                        lanes[u] = R::step(lanes[u], x[u], ib + e + int64_t(u) * GROUP);
                 }
-                for (; e < len; e += GROUP) lanes[0] = R::step(lanes[0], p[e], begin + e);
+                for (; e < len; e += GROUP) lanes[0] = R::step(lanes[0], p[e], ib + e);
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u) acc = R::combine(acc, lanes[u]);
             }

@@ -84,7 +84,7 @@ __global__ void reduce_identity_kernel(typename R::Out *res, RedMeta iter, int64
 // `final_pass` false: `res` is a dense scratch of Acc indexed [row][split].
 template <class R>
 int launch_inner(const typename R::In *arg, void *res, const RedMeta &iter, int64_t nrows, int64_t L,
-                 int64_t nsplit, int64_t chunk, bool final_pass, cudaStream_t stream)
+                 int64_t nsplit, int64_t chunk, bool final_pass, cudaStream_t stream, int64_t index_rows = 1)
 {
     constexpr int VEC = inner_vec<R>();
     constexpr int UNROLL = 4;
@@ -93,30 +93,49 @@ int launch_inner(const typename R::In *arg, void *res, const RedMeta &iter, int6
     if (len <= 16) {
         reduce_inner_kernel<R, 1, 1, UNROLL><<<red_grid(ceil_div(nitems, kRedThreads)), kRedThreads, 0,
                                               stream>>>(arg, res, iter, nrows, L, nsplit, chunk,
-                                                        final_pass);
+                                                        final_pass, index_rows);
         note_kernel("reduce_inner_thread");
     }
     else if (len <= 1024) {
         reduce_inner_kernel<R, VEC, 32, UNROLL>
             <<<red_grid(ceil_div(nitems, kRedThreads / 32)), kRedThreads, 0, stream>>>(
-                arg, res, iter, nrows, L, nsplit, chunk, final_pass);
+                arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
         note_kernel("reduce_inner_warp");
     }
     else {
         reduce_inner_kernel<R, VEC, 256, UNROLL><<<red_grid(nitems), kRedThreads, 0, stream>>>(
-            arg, res, iter, nrows, L, nsplit, chunk, final_pass);
+            arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
         note_kernel("reduce_inner_block");
     }
     return check_launch("reduce_inner");
 }
 
-// Complete inner reduction including the split decision and the second pass.
+// Complete inner reduction including the split decision and the second pass.  The last
+// reduction dimension is unit-stride; any further reduction dimensions ("outer" ones) are
+// treated like extra rows whose partial results are merged by the second pass, in order.
 template <class R>
 int run_inner(const RedPlan &plan, const typename R::In *arg, void *res, cudaStream_t stream)
 {
     using Acc = typename R::Acc;
-    const int64_t nrows = plan.niter, L = plan.nred;
-    RedMeta iter = make_meta(plan.iter_nd, plan.iter_shape, plan.iter_src, plan.iter_dst);
+    const int rlast = plan.red_nd - 1;
+    const int64_t L = plan.red_nd > 0 ? plan.red_shape[rlast] : 1;
+    int64_t n_outer = 1;
+    for (int i = 0; i < rlast; ++i) n_outer *= plan.red_shape[i];
+    const int64_t nrows = plan.niter * n_outer;
+    // rows = iteration dimensions followed by the outer reduction dimensions
+    int64_t shape[kMaxD], src[kMaxD], dst[kMaxD];
+    int nd = 0;
+    for (int i = 0; i < plan.iter_nd; ++i, ++nd) {
+        shape[nd] = plan.iter_shape[i];
+        src[nd] = plan.iter_src[i];
+        dst[nd] = plan.iter_dst[i];
+    }
+    for (int i = 0; i < rlast; ++i, ++nd) {
+        shape[nd] = plan.red_shape[i];
+        src[nd] = plan.red_src[i];
+        dst[nd] = 0;
+    }
+    RedMeta iter = make_meta(nd, shape, src, dst);
     int64_t nsplit = 1, chunk = L;
     const int64_t target = red_target_blocks();
     if (L > 16384 && nrows < target) {
@@ -125,17 +144,19 @@ int run_inner(const RedPlan &plan, const typename R::In *arg, void *res, cudaStr
         chunk = ceil_div(ceil_div(L, nsplit), 1024) * 1024;
         nsplit = ceil_div(L, chunk);
     }
-    if (nsplit <= 1) return launch_inner<R>(arg, res, iter, nrows, L, 1, L, true, stream);
+    if (nsplit <= 1 && n_outer == 1) return launch_inner<R>(arg, res, iter, nrows, L, 1, L, true, stream);
 
     void *scratch = nullptr;
     DPB_TRY(dpb_malloc(static_cast<size_t>(nrows * nsplit) * sizeof(Acc), stream, &scratch));
-    int st = launch_inner<R>(arg, scratch, iter, nrows, L, nsplit, chunk, false, stream);
+    int st = launch_inner<R>(arg, scratch, iter, nrows, L, nsplit, chunk, false, stream, n_outer);
     if (st == DPB_OK) {
+        // partials are laid out [result][outer row][split]: one dense row per result
+        const int64_t L2 = n_outer * nsplit;
         int64_t s2[kMaxD];
-        dense_strides(plan.iter_nd, plan.iter_shape, nsplit, s2);
+        dense_strides(plan.iter_nd, plan.iter_shape, L2, s2);
         RedMeta iter2 = make_meta(plan.iter_nd, plan.iter_shape, s2, plan.iter_dst);
-        st = launch_inner<typename R::Stage2>(static_cast<const Acc *>(scratch), res, iter2, nrows,
-                                              nsplit, 1, nsplit, true, stream);
+        st = launch_inner<typename R::Stage2>(static_cast<const Acc *>(scratch), res, iter2, plan.niter, L2, 1,
+                                              L2, true, stream);
     }
     dpb_free(scratch, stream);
     return st;

@@ -86,12 +86,19 @@ int make_red_plan(int iter_nd, const int64_t *iter_shape, const int64_t *iter_sr
     }
 
     if (nred == 0) return DPB_OK;
+    const bool outer_ok = plan.iter_nd >= 1 && plan.iter_src[plan.iter_nd - 1] == 1 &&
+                          plan.iter_dst[plan.iter_nd - 1] == 1 && plan.iter_shape[plan.iter_nd - 1] >= 16;
     if (plan.red_nd == 0 || (plan.red_nd == 1 && plan.red_src[0] == 1)) {
         plan.kind = RED_INNER;
     }
-    else if (plan.iter_nd >= 1 && plan.iter_src[plan.iter_nd - 1] == 1 &&
-             plan.iter_dst[plan.iter_nd - 1] == 1 && plan.iter_shape[plan.iter_nd - 1] >= 16) {
+    else if (outer_ok) {
         plan.kind = RED_OUTER;
+    }
+    else if (plan.red_src[plan.red_nd - 1] == 1 && plan.red_shape[plan.red_nd - 1] >= 32 &&
+             plan.iter_nd + plan.red_nd - 1 <= kMaxD) {
+        // several reduction dimensions, the innermost unit-stride: rows of the inner kernel,
+        // one per (result, outer reduction index)
+        plan.kind = RED_INNER;
     }
     else {
         plan.kind = RED_GENERIC;

@@ -136,6 +136,35 @@ def test_strided_and_permuted_inputs():
     assert _lib.last_kernel().startswith("reduce_inner")
 
 
+def test_several_reduction_axes_with_unit_stride_innermost():
+    """Reduction over (0, 2) of a C-contiguous array: rows of the inner kernel, one per
+    (result, index along axis 0), merged in order by a second pass."""
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    rng = np.random.default_rng(77)
+    for shape, dt in (((9, 40, 300), "f4"), ((3, 5, 40000), "f8"), ((6, 7, 64), "i4"), ((4, 3, 5, 130), "f8")):
+        x = (rng.normal(0, 1, shape) * 8).astype(dt)
+        x[tuple(s // 2 for s in shape)] = 1000          # a unique maximum
+        d = dev(x)
+        ax = (0, len(shape) - 1)
+        s = dp.sum(d, axis=ax)
+        assert _lib.last_kernel().startswith("reduce_inner"), _lib.last_kernel()
+        if dt[0] == "f":
+            check_float_sum(s.asnumpy(), x, ax, dt)
+        else:
+            np.testing.assert_array_equal(s.asnumpy(), orc.sum_int(x, axis=ax))
+        np.testing.assert_array_equal(dp.max(d, axis=ax).asnumpy(), x.max(axis=ax))
+        np.testing.assert_array_equal(dp.min(d, axis=ax).asnumpy(), x.min(axis=ax))
+        # flattened search over a view whose rows are not adjacent: (outer index, position) numbering
+        v, vx = d[:, 1:, 2:], x[:, 1:, 2:]
+        np.testing.assert_array_equal(dp.argmax(v).asnumpy(), vx.argmax())
+        np.testing.assert_array_equal(dp.argmin(v).asnumpy(), vx.argmin())
+        ties = np.zeros(shape, dt)
+        ties[1:, 1:, 2:] = 5                              # first occurrence wins across rows
+        np.testing.assert_array_equal(dp.argmax(dev(ties)[:, :, 1:]).asnumpy(), ties[:, :, 1:].argmax())
+
+
 def test_keepdims_out_and_dtype():
     import dpnp_b200 as dp
 
