@@ -248,16 +248,21 @@ def timed_steps(ev, fn, steps, flush=None):
     return ev.elapsed_ms(e0, e1)
 
 
-def median_time_ms(ev, fn, reps, warm=3):
+def median_time_ms(ev, fn, reps, warm=3, batch=1):
+    """Median over `reps` samples of the CUDA-event time of one call of fn.  A sample brackets
+    `batch` back-to-back calls and is divided by it: with one call per sample the device sits
+    idle between the first event and the launch while the host is still inside the call, and
+    that idle time would be charged to a kernel of a few hundred microseconds."""
     for _ in range(warm):
         fn()
     ts = []
     for _ in range(reps):
         e0, e1 = ev.new(), ev.new()
         ev.record(e0)
-        fn()
+        for _ in range(batch):
+            fn()
         ev.record(e1)
-        ts.append(ev.elapsed_ms(e0, e1))
+        ts.append(ev.elapsed_ms(e0, e1) / batch)
     ts.sort()
     return ts[len(ts) // 2]
 
@@ -477,7 +482,7 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     # fused Black-Scholes (one pass)
     pp, ps, pt = (a.get_array()._ptr for a in (price, strike, tt))
     pc, pq = call.get_array()._ptr, put.get_array()._ptr
-    ms = median_time_ms(ev, lambda: lib.dpb_black_scholes_f64(n, pp, ps, pt, RATE, VOL, pc, pq, S), 10)
+    ms = median_time_ms(ev, lambda: lib.dpb_black_scholes_f64(n, pp, ps, pt, RATE, VOL, pc, pq, S), 10, batch=4)
     rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms, "black_scholes_f64",
         "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option")
 
@@ -503,39 +508,40 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     rec("c1_add_f32_2^24_c_abi", 12 * m, ms)
     del sets
 
-    # further kernels of the path, one representative shape each (every rank runs its own copy)
+    # further kernels of the path, one representative shape each (every rank runs its own copy);
+    # 8 back-to-back calls per sample, operands of 512 MiB each (larger than L2)
     ne = 1 << 26
     xa, xb = dp.random.uniform(-1, 1, ne), dp.random.uniform(-1, 1, ne)
     xo = dp.empty(ne)
     cond = xa > 0.0
-    ms = median_time_ms(ev, lambda: dp.where(cond, xa, xb, out=xo), 10)
+    ms = median_time_ms(ev, lambda: dp.where(cond, xa, xb, out=xo), 10, batch=8)
     rec("where_f64_2^26", 25 * ne * world, ms, note="bool condition + two f64 operands + result")
-    ms = median_time_ms(ev, lambda: dp.where(cond, xa, 0.0, out=xo), 10)
+    ms = median_time_ms(ev, lambda: dp.where(cond, xa, 0.0, out=xo), 10, batch=8)
     rec("where_scalar_f64_2^26", 17 * ne * world, ms, note="second operand is a Python scalar (broadcast)")
     xf = dp.empty(ne, dtype="f4")
-    ms = median_time_ms(ev, lambda: dp.copyto(xf, xa, casting="same_kind"), 10)
+    ms = median_time_ms(ev, lambda: dp.copyto(xf, xa, casting="same_kind"), 10, batch=8)
     rec("copy_cast_f64_to_f32_2^26", 12 * ne * world, ms)
-    ms = median_time_ms(ev, lambda: dp.add(xa, xb, out=xa), 10)
+    ms = median_time_ms(ev, lambda: dp.add(xa, xb, out=xa), 10, batch=8)
     rec("inplace_add_f64_2^26", 24 * ne * world, ms)
-    ms = median_time_ms(ev, lambda: dp.multiply(xa, 0.25, out=xo), 10)
+    ms = median_time_ms(ev, lambda: dp.multiply(xa, 0.25, out=xo), 10, batch=8)
     rec("multiply_scalar_f64_2^26", 16 * ne * world, ms)
     del cond, xf
     mrows, mcols = 16384, 4096
     xm, xr = xa.reshape(mrows, mcols), xb[:mcols]
     xom = xo.reshape(mrows, mcols)
-    ms = median_time_ms(ev, lambda: dp.subtract(xm, xr, out=xom), 10)
+    ms = median_time_ms(ev, lambda: dp.subtract(xm, xr, out=xom), 10, batch=8)
     rec("row_broadcast_subtract_f64_16384x4096", 16 * ne * world, ms, note="matrix minus row vector")
     xv = xa.reshape(mrows, mcols)[:, 1:-1]
     xw = xo.reshape(mrows, mcols)[:, 1:-1]
-    ms = median_time_ms(ev, lambda: dp.multiply(xv, 2.0, out=xw), 10)
+    ms = median_time_ms(ev, lambda: dp.multiply(xv, 2.0, out=xw), 10, batch=8)
     rec("sliced_rows_multiply_f64_16384x4094", 16 * mrows * (mcols - 2) * world, ms,
         note="rows start off the 16-byte grid")
     x3 = xa.reshape(64, 1024, 1024)
-    ms = median_time_ms(ev, lambda: dp.sum(x3, axis=1), 10)
+    ms = median_time_ms(ev, lambda: dp.sum(x3, axis=1), 10, batch=8)
     rec("sum_middle_axis_f64_64x1024x1024", 8 * ne * world, ms)
-    ms = median_time_ms(ev, lambda: dp.sum(x3, axis=(0, 2)), 10)
+    ms = median_time_ms(ev, lambda: dp.sum(x3, axis=(0, 2)), 10, batch=8)
     rec("sum_axes02_f64_64x1024x1024", 8 * ne * world, ms)
-    ms = median_time_ms(ev, lambda: dp.argmax(x3, axis=0), 10)
+    ms = median_time_ms(ev, lambda: dp.argmax(x3, axis=0), 10, batch=8)
     rec("argmax_axis0_f64_64x1024x1024", 8 * ne * world, ms)
     del xa, xb, xo, xm, xr, xom, xv, xw, x3
 
@@ -552,12 +558,15 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
             q.wait()
             if dist is not None:
                 dist.barrier()
+            # one rank: 4 back-to-back calls per sample keep the device busy while the host
+            # is inside the next call; several ranks: one call, which ends in an exchange
+            batch = 4 if dist is None else 1
             e0, e1 = ev.new(), ev.new()
             ev.record(e0)
-            fn()
-            q.wait()
+            for _ in range(batch):
+                fn()
             ev.record(e1)
-            t = ev.elapsed_ms(e0, e1)
+            t = ev.elapsed_ms(e0, e1) / batch
             if dist is not None:
                 import torch
                 tt_ = torch.tensor([t], device="cuda", dtype=torch.float64)

@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(kEwThreads)
 template <class F, int VEC, int UNROLL>
 __global__ void __launch_bounds__(kEwThreads, 5)
     ew_rows_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> outer, int64_t L, unsigned inner_bcast,
-                   int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div)
+                   int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div,
+                   int head)
 {
     using In0 = typename F::In0;
     using In1 = typename F::In1;
@@ -186,11 +187,32 @@ __global__ void __launch_bounds__(kEwThreads, 5)
         if constexpr (F::NIN >= 2) { if (inner_bcast & 2u) sb = b[0]; }
         if constexpr (F::NIN >= 3) { if (inner_bcast & 4u) sc = c[0]; }
 
+        // Rows that start `VEC - head` elements past a 16-byte boundary in every operand:
+        // the first `head` elements go one by one, the rest is on the vector grid.
+        if (head) {
+            if (chunk == 0) {
+                for (int e = tx; e < head; e += TX) {
+                    In0 x = sa;
+                    In1 y = sb;
+                    In2 z = sc;
+                    if constexpr (F::NIN >= 1) { if (!(inner_bcast & 1u)) x = a[e]; }
+                    if constexpr (F::NIN >= 2) { if (!(inner_bcast & 2u)) y = b[e]; }
+                    if constexpr (F::NIN >= 3) { if (!(inner_bcast & 4u)) z = c[e]; }
+                    o[e] = ew_apply(f, x, y, z);
+                }
+            }
+            if constexpr (F::NIN >= 1) { if (!(inner_bcast & 1u)) a += head; }
+            if constexpr (F::NIN >= 2) { if (!(inner_bcast & 2u)) b += head; }
+            if constexpr (F::NIN >= 3) { if (!(inner_bcast & 4u)) c += head; }
+            o += head;
+        }
+        const int64_t Lb = L - head;
+
         const int64_t v0 = chunk * (int64_t(TX) * UNROLL) + tx;  // first vector index
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int64_t j = (v0 + int64_t(u) * TX) * VEC;  // first element
-            if (j + VEC <= L) {
+            if (j + VEC <= Lb) {
                 vec_t<In0, VEC> va;
                 vec_t<In1, VEC> vb;
                 vec_t<In2, VEC> vc;
@@ -211,7 +233,7 @@ __global__ void __launch_bounds__(kEwThreads, 5)
                 store_vec(o + j, r);
             }
             else {
-                for (int64_t e = j; e < L; ++e) {
+                for (int64_t e = j; e < Lb; ++e) {
                     In0 x = sa;
                     In1 y = sb;
                     In2 z = sc;
@@ -643,17 +665,24 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         unsigned inner_bcast = 0;
         for (int k = 0; k < NIN; ++k)
             if (plan.strides[k][last] == 0) inner_bcast |= (1u << k);
-        // 16-byte accesses need aligned row starts in every unit-stride operand
-        bool aligned = is_aligned(out, sizeof(Out) * VEC);
+        // 16-byte accesses need row starts that sit at one common element position within
+        // a 16-byte group in every unit-stride operand; rows that start off the boundary
+        // take their first `head` elements one by one
+        auto misalign = [](const void *ptr, size_t elem) {
+            return static_cast<int>((reinterpret_cast<uintptr_t>(ptr) / elem) % VEC);
+        };
+        bool aligned = VEC > 1;
+        const int mis = misalign(out, sizeof(Out));
         for (int i = 0; i < last; ++i) aligned = aligned && (plan.strides[NARR - 1][i] % VEC == 0);
         for (int k = 0; k < NIN; ++k) {
             if (inner_bcast & (1u << k)) continue;
-            aligned = aligned && is_aligned(in[k], in_sizes[k] * VEC);
+            aligned = aligned && misalign(in[k], in_sizes[k]) == mis;
             for (int i = 0; i < last; ++i) aligned = aligned && (plan.strides[k][i] % VEC == 0);
         }
-        const int vec = (aligned && VEC > 1) ? VEC : 1;
+        const int vec = aligned ? VEC : 1;
+        const int head = aligned ? static_cast<int>(std::min<int64_t>((VEC - mis) % VEC, L)) : 0;
         constexpr int UNROLL = 4;
-        const int64_t nvec = ceil_div(L, vec);
+        const int64_t nvec = std::max<int64_t>(1, ceil_div(L - head, vec));
         int tx_log2 = 0;
         while ((1 << tx_log2) < kEwThreads && (int64_t(1) << tx_log2) * UNROLL < nvec) ++tx_log2;
         const int TX = 1 << tx_log2, TY = kEwThreads >> tx_log2;
@@ -662,12 +691,12 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         const FastDiv32 chunk_div(static_cast<uint32_t>(chunks < (int64_t(1) << 31) ? chunks : 1));
         if (vec > 1) {
             ew_rows_kernel<F, VEC, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div);
-            note_kernel("ew_rows_vec");
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, head);
+            note_kernel(head ? "ew_rows_vec_head" : "ew_rows_vec");
         }
         else {
             ew_rows_kernel<F, 1, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div);
+                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, 0);
             note_kernel("ew_rows_scalar");
         }
         return check_launch("ew_rows");

@@ -207,6 +207,44 @@ def test_strided_broadcast_and_transposed_operands():
     np.testing.assert_array_equal((w + w).asnumpy(), 2 * x6[:, ::2, :, ::-1, :, ::3])
 
 
+def test_rows_that_start_off_the_16_byte_grid():
+    """Rows whose first element sits at the same position within a 16-byte group in every
+    operand are processed as a few leading elements plus aligned vectors; any other
+    combination of starts takes the element-wise path.  Both must give the same bits."""
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    rng = np.random.default_rng(31)
+    for dt, cols in (("f8", 64), ("f4", 72), ("u1", 96), ("i2", 80)):
+        a, b = rand(rng, dt, (33, cols)), rand(rng, dt, (33, cols), 1, 20)
+        da, db = dev(a), dev(b)
+        out = dp.zeros((33, cols), dtype=dt)
+        vec = 16 // np.dtype(dt).itemsize
+        for lo in range(0, vec + 1):
+            for hi in (cols, cols - 1, cols - vec - 1):
+                dp.add(da[:, lo:hi], db[:, lo:hi], out=out[:, lo:hi])
+                if 0 < lo < vec:
+                    assert _lib.last_kernel() == "ew_rows_vec_head", (_lib.last_kernel(), dt, lo, hi)
+                np.testing.assert_array_equal(out.asnumpy()[:, lo:hi], a[:, lo:hi] + b[:, lo:hi])
+                dp.multiply(da[:, lo:hi], 3, out=out[:, lo:hi])
+                np.testing.assert_array_equal(out.asnumpy()[:, lo:hi], a[:, lo:hi] * np.dtype(dt).type(3))
+        # starts that differ between the operands: one element at a time
+        dp.add(da[:, 1:-1], db[:, 2:], out=out[:, :-2])
+        assert _lib.last_kernel() == "ew_rows_scalar"
+        np.testing.assert_array_equal(out.asnumpy()[:, :-2], a[:, 1:-1] + b[:, 2:])
+        # a row shorter than the leading part, and a flat array that starts off the grid
+        dp.add(da[:, 1:2], db[:, 1:2], out=out[:, 1:2])
+        np.testing.assert_array_equal(out.asnumpy()[:, 1:2], a[:, 1:2] + b[:, 1:2])
+        fa, fb = da.reshape(-1), db.reshape(-1)
+        np.testing.assert_array_equal(dp.add(fa[1:], fb[1:], out=fa[1:].copy()).asnumpy(),
+                                      a.reshape(-1)[1:] + b.reshape(-1)[1:])
+    # mixed element sizes: f64 rows into an f32 result
+    x = rng.normal(0, 1, (20, 50))
+    o32 = dp.zeros((20, 50), dtype="f4")
+    dp.copyto(o32[:, 1:], dev(x)[:, 1:], casting="same_kind")
+    np.testing.assert_array_equal(o32.asnumpy()[:, 1:], x[:, 1:].astype("f4"))
+
+
 def test_output_layout_follows_order_k():
     import dpnp_b200 as dp
 
