@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(kRedThreads)
 // as [slab][batch][C].
 constexpr int kOuterRows = 8;
 
-template <class R, int VEC, int UNROLL>
+template <class R, int VEC, int UNROLL, int ROWS>
 __global__ void __launch_bounds__(kRedThreads)
     reduce_outer_kernel(const typename R::In *arg, void *res, RedMeta batch, RedMeta red, int64_t C,
                         int64_t nred, int64_t nbatch, int64_t nslab, int64_t slab_len,
@@ -269,8 +269,11 @@ __global__ void __launch_bounds__(kRedThreads)
 {
     using In = typename R::In;
     using Acc = typename R::Acc;
-    __shared__ Acc smem[kOuterRows][32][VEC];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    // ROWS thread rows share the reduction range of a column group; ROWS == 1 gives every
+    // thread its own columns and needs no exchange through shared memory
+    constexpr int TXW = kRedThreads / ROWS;
+    __shared__ Acc smem[ROWS > 1 ? ROWS : 1][ROWS > 1 ? TXW : 1][VEC];
+    const int tx = threadIdx.x % TXW, ty = threadIdx.x / TXW;
     const int64_t nwork = nbatch * nslab * ncolgroups;
 
     for (int64_t w = blockIdx.x; w < nwork; w += gridDim.x) {
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(kRedThreads)
         const int64_t ws = w / ncolgroups;
         const int64_t slab = ws % nslab;
         const int64_t b = ws / nslab;
-        const int64_t col = (cg * 32 + tx) * VEC;
+        const int64_t col = (cg * TXW + tx) * VEC;
         const bool active = col < C;
         int64_t b_src = 0, b_dst = 0;
         red_offsets(batch, b, b_src, b_dst);
@@ -293,11 +296,11 @@ __global__ void __launch_bounds__(kRedThreads)
             const bool simple = (red.nd == 1);
             const int64_t rs = red.strides[0][0];
             int64_t r = r_begin + ty;
-            for (; r + int64_t(UNROLL - 1) * kOuterRows < r_end; r += int64_t(UNROLL) * kOuterRows) {
+            for (; r + int64_t(UNROLL - 1) * ROWS < r_end; r += int64_t(UNROLL) * ROWS) {
                 vec_t<In, VEC> x[UNROLL];
 #pragma unroll
                 for (int u = 0; u < UNROLL; ++u) {
-                    const int64_t rr = r + int64_t(u) * kOuterRows;
+                    const int64_t rr = r + int64_t(u) * ROWS;
                     int64_t off, unused;
                     if (simple) off = rr * rs;
                     else red_offsets(red, rr, off, unused);
@@ -307,9 +310,9 @@ __global__ void __launch_bounds__(kRedThreads)
                 for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
                     for (int k = 0; k < VEC; ++k)
-                        lanes[k] = R::step(lanes[k], x[u].v[k], r + int64_t(u) * kOuterRows);
+                        lanes[k] = R::step(lanes[k], x[u].v[k], r + int64_t(u) * ROWS);
             }
-            for (; r < r_end; r += kOuterRows) {
+            for (; r < r_end; r += ROWS) {
                 int64_t off, unused;
                 if (simple) off = r * rs;
                 else red_offsets(red, r, off, unused);
@@ -318,16 +321,21 @@ __global__ void __launch_bounds__(kRedThreads)
                 for (int k = 0; k < VEC; ++k) lanes[k] = R::step(lanes[k], x.v[k], r);
             }
         }
-        __syncthreads();
+        if constexpr (ROWS > 1) {
+            __syncthreads();
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) smem[ty][tx][k] = lanes[k];
-        __syncthreads();
+            for (int k = 0; k < VEC; ++k) smem[ty][tx][k] = lanes[k];
+            __syncthreads();
+        }
         if (ty == 0 && active) {
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
-                Acc a = smem[0][tx][k];
+                Acc a = lanes[k];
+                if constexpr (ROWS > 1) {
+                    a = smem[0][tx][k];
 #pragma unroll
-                for (int j = 1; j < kOuterRows; ++j) a = R::combine(a, smem[j][tx][k]);
+                    for (int j = 1; j < ROWS; ++j) a = R::combine(a, smem[j][tx][k]);
+                }
                 if (final_pass) red_store<R>(res, b_dst + col + k, a, true);
                 else red_store<R>(res, (slab * nbatch + b) * C + col + k, a, false);
             }

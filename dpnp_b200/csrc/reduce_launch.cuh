@@ -163,23 +163,40 @@ int run_inner(const RedPlan &plan, const typename R::In *arg, void *res, cudaStr
 }
 
 // ------------------------------------------------------------------ outer
+// `columns_per_thread`: every thread owns its columns over the whole reduction range (many
+// columns, short range); otherwise 8 thread rows share the range of a 32-thread column group.
 template <class R>
 int launch_outer(const typename R::In *arg, void *res, const RedMeta &batch, const RedMeta &red,
                  int64_t C, int64_t nred, int64_t nbatch, int64_t nslab, int64_t slab_len,
-                 bool vector_ok, bool final_pass, cudaStream_t stream)
+                 bool vector_ok, bool final_pass, cudaStream_t stream, bool columns_per_thread = false)
 {
     constexpr int VEC = outer_vec<R>();
     constexpr int UNROLL = 4;
-    if (vector_ok && VEC > 1) {
+    const bool vec = vector_ok && VEC > 1;
+    if (columns_per_thread) {
+        const int64_t ncg = ceil_div(C, int64_t(kRedThreads) * (vec ? VEC : 1));
+        const int64_t nblocks = nbatch * nslab * ncg;
+        const int grid = static_cast<int>(std::min<int64_t>(nblocks, int64_t(1) << 30));
+        if (vec)
+            reduce_outer_kernel<R, VEC, 2 * UNROLL, 1><<<grid, kRedThreads, 0, stream>>>(
+                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        else
+            reduce_outer_kernel<R, 1, 2 * UNROLL, 1><<<grid, kRedThreads, 0, stream>>>(
+                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        note_kernel(vec ? "reduce_outer_cols_vec" : "reduce_outer_cols_scalar");
+    }
+    else if (vec) {
         const int64_t ncg = ceil_div(C, 32 * VEC);
-        reduce_outer_kernel<R, VEC, UNROLL><<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
-            arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        reduce_outer_kernel<R, VEC, UNROLL, kOuterRows>
+            <<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
+                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
         note_kernel("reduce_outer_vec");
     }
     else {
         const int64_t ncg = ceil_div(C, 32);
-        reduce_outer_kernel<R, 1, UNROLL><<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
-            arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        reduce_outer_kernel<R, 1, UNROLL, kOuterRows>
+            <<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
+                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
         note_kernel("reduce_outer_scalar");
     }
     return check_launch("reduce_outer");
@@ -203,10 +220,14 @@ int run_outer(const RedPlan &plan, const typename R::In *arg, void *res, cudaStr
     for (int i = 0; i < plan.red_nd; ++i) vector_ok = vector_ok && (plan.red_src[i] % VEC == 0);
     const int vec = (vector_ok && VEC > 1) ? VEC : 1;
 
-    const int64_t work0 = nbatch * ceil_div(C, 32 * vec);
     const int64_t target = red_target_blocks();
+    // enough columns to give every thread its own: no sharing of the reduction range
+    if (nbatch * ceil_div(C, int64_t(kRedThreads) * vec) >= 4 * int64_t(device_props().sm_count))
+        return launch_outer<R>(arg, res, batch, red, C, nred, nbatch, 1, nred, vector_ok, true, stream, true);
+
+    const int64_t work0 = nbatch * ceil_div(C, 32 * vec);
     int64_t nslab = 1, slab_len = nred;
-    if (work0 < target && nred >= 128) {
+    if (work0 * 2 <= target && nred >= 128) {
         nslab = std::min<int64_t>(ceil_div(target, work0), nred / 64);
         nslab = std::max<int64_t>(1, std::min<int64_t>(nslab, 1024));
         slab_len = ceil_div(ceil_div(nred, nslab), 32) * 32;

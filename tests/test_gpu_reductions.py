@@ -165,6 +165,33 @@ def test_several_reduction_axes_with_unit_stride_innermost():
         np.testing.assert_array_equal(dp.argmax(dev(ties)[:, :, 1:]).asnumpy(), ties[:, :, 1:].argmax())
 
 
+def test_leading_axis_with_many_columns_gives_each_thread_its_columns():
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    rng = np.random.default_rng(78)
+    for shape, dt, kernel in (((64, 1 << 19), "f8", "reduce_outer_cols_vec"),
+                              ((19, 700003), "f4", "reduce_outer_cols_scalar"),
+                              ((3, 33, 1 << 18), "i4", "reduce_outer_cols_vec")):
+        x = (rng.normal(0, 1, shape) * 50).astype(dt)
+        d = dev(x)
+        s = dp.sum(d, axis=0)
+        assert _lib.last_kernel() == kernel, _lib.last_kernel()
+        if dt[0] == "f":
+            check_float_sum(s.asnumpy(), x, 0, dt)
+        else:
+            np.testing.assert_array_equal(s.asnumpy(), orc.sum_int(x, axis=0))
+        np.testing.assert_array_equal(dp.max(d, axis=0).asnumpy(), x.max(axis=0))
+        x[::2] = np.round(x[::2] / 25)                  # many ties: first occurrence must win
+        d = dev(x)
+        np.testing.assert_array_equal(dp.argmax(d, axis=0).asnumpy(), x.argmax(axis=0))
+        assert _lib.last_kernel() == kernel
+        np.testing.assert_array_equal(dp.argmin(d, axis=0).asnumpy(), x.argmin(axis=0))
+        if len(shape) == 3:
+            np.testing.assert_array_equal(dp.max(d, axis=1).asnumpy(), x.max(axis=1))
+            np.testing.assert_array_equal(dp.argmax(d, axis=1).asnumpy(), x.argmax(axis=1))
+
+
 def test_keepdims_out_and_dtype():
     import dpnp_b200 as dp
 
