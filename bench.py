@@ -486,6 +486,14 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms, "black_scholes_f64",
         "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option")
 
+    # the same chain through the general front-end: traced once, then one interpreted launch
+    chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
+    ms = median_time_ms(ev, lambda: chain(price, strike, tt, call, put), 10, batch=4)
+    if chain.fused_calls == 0:
+        raise RuntimeError(f"the Black-Scholes chain was not fused: {chain.last_reason}")
+    rec("c2_black_scholes_fuse_decorator_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms,
+        note="dpnp_b200.fuse: the 26-call chain as a register-machine program, one launch")
+
     # C1: add f32 2^24, rotating over 4 buffer sets (768 MiB > L2)
     m = 1 << 24
     sets = [(dp.random.uniform(-1, 1, m, dtype="f4"), dp.random.uniform(-1, 1, m, dtype="f4"),

@@ -5,7 +5,7 @@ reduction-over-axis engine) on NVIDIA B200, behind the dpnp Python API.
 elementwise and reduction paths need: ``ndarray``, creation and view functions,
 the ufunc objects (add, subtract, multiply, divide, negative, exp, log, sqrt,
 erf, comparisons, ...), ``where``, and the reductions sum, prod, mean, max, min,
-argmax, argmin.  All compute runs in hand-written CUDA kernels of
+argmax, argmin, plus ``fuse`` (a chain of elementwise calls as one launch).  All compute runs in hand-written CUDA kernels of
 ``libdpnp_b200.so``; there is no CPU fallback.
 """
 
@@ -18,6 +18,7 @@ from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, arg
                      get_result_array, get_usm_ndarray, get_usm_ndarray_or_scalar,
                      is_supported_array_type, max, mean, min, ones, ones_like, prod, ravel, reshape,
                      squeeze, sum, transpose, where, zeros, zeros_like)
+from ._fusion import fuse
 from ._ufuncs import (DPNPBinaryFunc, DPNPUnaryFunc, abs, absolute, add, ceil, cos, divide, equal, erf,
                       exp, expm1, floor, greater, greater_equal, isfinite, isinf, isnan, less,
                       less_equal, log, log1p, logical_and, logical_not, logical_or, maximum, minimum,

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from . import _fusion
 from . import tensor as dpt
 from .dpnp_array import dpnp_array
 from .tensor import _tensor_impl as ti
@@ -258,6 +259,8 @@ def where(condition, x=None, y=None, /, *, order="K", out=None):
         raise ValueError("Must provide both 'x' and 'y' or neither.")
     if missing == 2:
         raise NotImplementedError("where(condition) alone (nonzero) is not provided by the elementwise path")
+    if _fusion.is_traced(condition, x, y):         # inside a function that is being fused
+        return _fusion.trace_where(condition, x, y, out)
     cond = get_usm_ndarray(condition)
     xu = get_usm_ndarray_or_scalar(x)
     yu = get_usm_ndarray_or_scalar(y)

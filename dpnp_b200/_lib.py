@@ -150,6 +150,7 @@ PROTOTYPES = {
     "dpb_reduction_over_axis": (_i, [_i, _parr, _i, _parr, _vp]),
     "dpb_search_over_axis": (_i, [_i, _parr, _i, _parr, _vp]),
     "dpb_black_scholes_f64": (_i, [_i64, _vp, _vp, _vp, _dbl, _dbl, _vp, _vp, _vp]),
+    "dpb_fused_elementwise": (_i, [_vp, _i64, _vp]),
     "dpb_random_uniform": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),
     "dpb_random_normal": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),
     "dpb_last_kernel": (C.c_char_p, []),

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from . import _fusion
 from . import tensor as dpt
 from .dpnp_array import dpnp_array
 from .tensor import _elementwise_funcs as ef
@@ -67,6 +68,10 @@ class DPNPUnaryFunc(UnaryElementwiseFunc):
 
     def __call__(self, x, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
         _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+        if type(x) is _fusion.FusedValue:          # inside a function that is being fused
+            if dtype is not None:
+                raise _fusion.FusionUnsupported("dtype= inside a fused function")
+            return _fusion.trace_unary(self.name_, x, out)
         if not _is_array(x):
             raise TypeError(f"Input array must be any of supported type, but got {type(x)}")
         order = _norm_order(order)
@@ -90,6 +95,11 @@ class DPNPBinaryFunc(BinaryElementwiseFunc):
         self.__name__ = "DPNPBinaryFunc"
 
     def __call__(self, x1, x2, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
+        if _fusion.is_traced(x1, x2):              # inside a function that is being fused
+            _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+            if dtype is not None:
+                raise _fusion.FusionUnsupported("dtype= inside a fused function")
+            return _fusion.trace_binary(self.name_, x1, x2, out)
         for x in (x1, x2):
             if not (_is_array(x) or _is_scalar(x)):
                 raise TypeError(f"An array must be any of supported type, but got {type(x)}")

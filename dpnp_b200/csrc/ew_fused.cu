@@ -1,0 +1,304 @@
+// Fused elementwise chains: one launch evaluates a whole expression graph per element.
+//
+// The reference has no fusion: every ufunc call of a chain such as
+// examples/example_bs.py:50-78 is one kernel that reads and writes full arrays
+// (dpnp/dpnp_algo/dpnp_elementwise_common.py:81-235,537-739 calls straight into the
+// per-op implementations).  Here a chain is handed over as a small register-machine
+// program; the kernel interprets it with the operators of the per-op engine (the same
+// device functions, so every intermediate value has the bits the unfused chain gives)
+// and touches global memory only for the chain's inputs and outputs.
+//
+// Execution model: a block owns a tile of kFusedThreads * K consecutive elements.  A thread
+// holds K elements of every virtual register in shared memory, laid out
+// [register][k][thread] (bank-conflict free), plus one "accumulator" -- the result of
+// the previous instruction -- in real registers, so that chains of dependent operations
+// do not bounce through shared memory.  Every thread of the grid executes the same
+// instruction stream: branches on the opcode are uniform.
+
+#include <cstring>
+
+#include "common.cuh"
+#include "ew_ops.cuh"
+
+namespace dpb {
+
+constexpr int kFusedThreads = 128;
+constexpr int kFusedK = 8;             // elements per thread and register
+constexpr int kFusedMaxInstr = 192;
+constexpr int kFusedMaxImm = 48;
+constexpr int kFusedMaxIn = 12;
+constexpr int kFusedMaxOut = 8;
+constexpr int kFusedMaxReg = 24;
+
+// operand encoding (8 bits)
+constexpr unsigned kOpndImm = 64;      // 64 + i: immediate i
+constexpr unsigned kOpndAcc = 255;     // result of the previous instruction
+constexpr unsigned kNoDst = 255;       // result stays in the accumulator only
+
+struct FusedParams {
+    int32_t n_instr;
+    int32_t vector_io;                  // every array pointer is 16-byte aligned
+    uint64_t code[kFusedMaxInstr];      // op | dst << 8 | a << 16 | b << 24 | c << 32
+    double imm[kFusedMaxImm];
+    const void *in[kFusedMaxIn];
+    int32_t in_scalar[kFusedMaxIn];     // input is one element, broadcast
+    void *out[kFusedMaxOut];
+};
+
+template <class T> DPB_D T as_flag(bool_t b) { return b.v ? T(1) : T(0); }
+
+// One decode per instruction: the opcode selects a loop over the thread's K elements.
+#define DPB_FUSED_UN(CODE, EXPR)                                   \
+    case CODE:                                                     \
+        _Pragma("unroll") for (int k = 0; k < K; ++k) { const T x = a[k]; r[k] = (EXPR); } \
+        break;
+#define DPB_FUSED_BIN(CODE, EXPR)                                  \
+    case CODE:                                                     \
+        _Pragma("unroll") for (int k = 0; k < K; ++k) { const T x = a[k]; const T y = b[k]; r[k] = (EXPR); } \
+        break;
+
+template <class T, int K> DPB_D void fused_unary(int op, const T (&a)[K], T (&r)[K])
+{
+    switch (op) {
+        DPB_FUSED_UN(DPB_FUSED_NEGATIVE, NegativeOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_ABS, AbsOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_EXP, ExpOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_LOG, LogOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_SQRT, SqrtOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_ERF, ErfOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_SQUARE, SquareOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_RECIPROCAL, ReciprocalOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_SIN, SinOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_COS, CosOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_TANH, TanhOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_EXPM1, Expm1Op<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_LOG1P, Log1pOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_FLOOR, FloorOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_CEIL, CeilOp<T>::apply(x))
+        DPB_FUSED_UN(DPB_FUSED_SIGN, SignOp<T>::apply(x))
+    default:  // DPB_FUSED_POSITIVE, DPB_FUSED_MOVE
+#pragma unroll
+        for (int k = 0; k < K; ++k) r[k] = a[k];
+    }
+}
+
+template <class T, int K> DPB_D void fused_binary(int op, const T (&a)[K], const T (&b)[K], T (&r)[K])
+{
+    switch (op) {
+        DPB_FUSED_BIN(DPB_FUSED_ADD, (AddOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_SUBTRACT, (SubtractOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_MULTIPLY, (MultiplyOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_DIVIDE, (TrueDivideOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_MAXIMUM, (MaximumOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_MINIMUM, (MinimumOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_POW, (PowOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_LESS, as_flag<T>(LessOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_LESS_EQUAL, as_flag<T>(LessEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_GREATER, as_flag<T>(GreaterOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_GREATER_EQUAL, as_flag<T>(GreaterEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_EQUAL, as_flag<T>(EqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_NOT_EQUAL, as_flag<T>(NotEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BIN(DPB_FUSED_LOGICAL_AND, ((x != T(0) && y != T(0)) ? T(1) : T(0)))
+        DPB_FUSED_BIN(DPB_FUSED_LOGICAL_OR, ((x != T(0) || y != T(0)) ? T(1) : T(0)))
+    default:
+#pragma unroll
+        for (int k = 0; k < K; ++k) r[k] = a[k];
+    }
+}
+#undef DPB_FUSED_UN
+#undef DPB_FUSED_BIN
+
+template <class T>
+__global__ void __launch_bounds__(kFusedThreads)
+    ew_fused_kernel(const __grid_constant__ FusedParams prm, int64_t n)
+{
+    constexpr int K = kFusedK;
+    constexpr int VW = 16 / sizeof(T);  // elements per 16-byte access
+    extern __shared__ __align__(16) unsigned char fused_smem[];
+    T *regs = reinterpret_cast<T *>(fused_smem);
+    const int tid = threadIdx.x;
+    const int64_t base = (int64_t(blockIdx.x) * kFusedThreads + tid) * K;  // first element of the thread
+    if (base >= n) return;  // no block-wide barrier below: every thread works on its own slots
+    const bool whole = base + K <= n;
+
+    T acc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc[k] = T(0);
+
+    auto fetch = [&](unsigned x, T(&v)[K]) {
+        if (x == kOpndAcc) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) v[k] = acc[k];
+        }
+        else if (x >= kOpndImm) {
+            const T c = static_cast<T>(prm.imm[x - kOpndImm]);
+#pragma unroll
+            for (int k = 0; k < K; ++k) v[k] = c;
+        }
+        else {
+#pragma unroll
+            for (int k = 0; k < K; ++k) v[k] = regs[(x * K + k) * kFusedThreads + tid];
+        }
+    };
+
+    for (int pc = 0; pc < prm.n_instr; ++pc) {
+        const uint64_t w = prm.code[pc];
+        const int op = static_cast<int>(w & 0xff);
+        const unsigned dst = static_cast<unsigned>((w >> 8) & 0xff);
+        const unsigned oa = static_cast<unsigned>((w >> 16) & 0xff);
+        const unsigned ob = static_cast<unsigned>((w >> 24) & 0xff);
+        const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
+        T r[K];
+        if (op == DPB_FUSED_LOAD) {
+            const T *src = static_cast<const T *>(prm.in[oa]);
+            if (prm.in_scalar[oa]) {
+                const T c = src[0];
+#pragma unroll
+                for (int k = 0; k < K; ++k) r[k] = c;
+            }
+            else if (whole && prm.vector_io) {
+#pragma unroll
+                for (int k = 0; k < K; k += VW) {
+                    vec_t<T, VW> x = load_vec<vec_t<T, VW>>(src + base + k);
+#pragma unroll
+                    for (int j = 0; j < VW; ++j) r[k + j] = x.v[j];
+                }
+            }
+            else {
+#pragma unroll
+                for (int k = 0; k < K; ++k) r[k] = (base + k < n) ? src[base + k] : T(0);
+            }
+        }
+        else if (op == DPB_FUSED_STORE) {
+            T v[K];
+            fetch(oa, v);
+            T *dstp = static_cast<T *>(prm.out[ob]);
+            if (whole && prm.vector_io) {
+#pragma unroll
+                for (int k = 0; k < K; k += VW) {
+                    vec_t<T, VW> x;
+#pragma unroll
+                    for (int j = 0; j < VW; ++j) x.v[j] = v[k + j];
+                    store_vec(dstp + base + k, x);
+                }
+            }
+            else {
+#pragma unroll
+                for (int k = 0; k < K; ++k)
+                    if (base + k < n) dstp[base + k] = v[k];
+            }
+            continue;  // a store leaves the accumulator as it is
+        }
+        else if (op == DPB_FUSED_SELECT) {
+            T c[K], a[K], b[K];
+            fetch(oa, c);
+            fetch(ob, a);
+            fetch(oc, b);
+#pragma unroll
+            for (int k = 0; k < K; ++k) r[k] = (c[k] != T(0)) ? a[k] : b[k];
+        }
+        else if (op < DPB_FUSED_FIRST_BINARY) {
+            T a[K];
+            fetch(oa, a);
+            fused_unary<T, K>(op, a, r);
+        }
+        else {
+            T a[K], b[K];
+            fetch(oa, a);
+            fetch(ob, b);
+            fused_binary<T, K>(op, a, b, r);
+        }
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc[k] = r[k];
+        if (dst != kNoDst) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) regs[(dst * K + k) * kFusedThreads + tid] = r[k];
+        }
+    }
+}
+
+namespace {
+
+bool operand_ok(unsigned x, int n_reg, int n_imm, bool first)
+{
+    if (x == kOpndAcc) return !first;
+    if (x >= kOpndImm) return static_cast<int>(x - kOpndImm) < n_imm;
+    return static_cast<int>(x) < n_reg;
+}
+
+}  // namespace
+}  // namespace dpb
+
+using namespace dpb;
+
+extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, void *stream)
+{
+    if (!prog) return set_error(DPB_ERR_VALUE, "fused program is null");
+    if (prog->typenum != DPB_FLOAT && prog->typenum != DPB_DOUBLE)
+        return set_error(DPB_ERR_TYPE, "fused programs compute in float32 or float64");
+    if (prog->n_instr < 0 || prog->n_instr > kFusedMaxInstr || prog->n_imm < 0 || prog->n_imm > kFusedMaxImm ||
+        prog->n_in < 0 || prog->n_in > kFusedMaxIn || prog->n_out < 0 || prog->n_out > kFusedMaxOut ||
+        prog->n_reg < 0 || prog->n_reg > kFusedMaxReg)
+        return set_error(DPB_ERR_VALUE, "fused program exceeds the limits of the interpreter "
+                                        "(192 instructions, 48 immediates, 12 inputs, 8 outputs, 24 registers)");
+    if (n < 0) return set_error(DPB_ERR_VALUE, "negative element count");
+    FusedParams prm;
+    std::memset(&prm, 0, sizeof(prm));
+    prm.n_instr = prog->n_instr;
+    bool aligned = true;
+    for (int i = 0; i < prog->n_in; ++i) {
+        if (!prog->in[i]) return set_error(DPB_ERR_VALUE, "fused program: null input pointer");
+        prm.in[i] = prog->in[i];
+        prm.in_scalar[i] = prog->in_is_scalar ? prog->in_is_scalar[i] : 0;
+        if (!prm.in_scalar[i]) aligned = aligned && is_aligned(prog->in[i], 16);
+    }
+    for (int i = 0; i < prog->n_out; ++i) {
+        if (!prog->out[i]) return set_error(DPB_ERR_VALUE, "fused program: null output pointer");
+        prm.out[i] = prog->out[i];
+        aligned = aligned && is_aligned(prog->out[i], 16);
+    }
+    prm.vector_io = aligned ? 1 : 0;
+    for (int i = 0; i < prog->n_imm; ++i) prm.imm[i] = prog->imm[i];
+    // every index the kernel will use is checked here, once, on the host
+    for (int pc = 0; pc < prog->n_instr; ++pc) {
+        const uint64_t w = prog->code[pc];
+        const int op = static_cast<int>(w & 0xff);
+        const unsigned dst = static_cast<unsigned>((w >> 8) & 0xff);
+        const unsigned oa = static_cast<unsigned>((w >> 16) & 0xff);
+        const unsigned ob = static_cast<unsigned>((w >> 24) & 0xff);
+        const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
+        const bool first = pc == 0;
+        bool ok = op >= 0 && op < DPB_FUSED_OP_COUNT;
+        if (ok && op == DPB_FUSED_LOAD) ok = static_cast<int>(oa) < prog->n_in;
+        else if (ok && op == DPB_FUSED_STORE)
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && static_cast<int>(ob) < prog->n_out;
+        else if (ok && op == DPB_FUSED_SELECT)
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && operand_ok(ob, prog->n_reg, prog->n_imm, first) &&
+                 operand_ok(oc, prog->n_reg, prog->n_imm, first);
+        else if (ok && op < DPB_FUSED_FIRST_BINARY) ok = operand_ok(oa, prog->n_reg, prog->n_imm, first);
+        else if (ok)
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && operand_ok(ob, prog->n_reg, prog->n_imm, first);
+        if (ok && op != DPB_FUSED_STORE) ok = dst == kNoDst || static_cast<int>(dst) < prog->n_reg;
+        if (!ok) return set_error(DPB_ERR_VALUE, "fused program: malformed instruction");
+        prm.code[pc] = w;
+    }
+    if (n == 0 || prog->n_instr == 0) return DPB_OK;
+    const size_t elem = prog->typenum == DPB_DOUBLE ? 8 : 4;
+    const size_t smem = static_cast<size_t>(prog->n_reg > 0 ? prog->n_reg : 1) * kFusedK * kFusedThreads * elem;
+    const int64_t tile = int64_t(kFusedThreads) * kFusedK;
+    const int64_t blocks = (n + tile - 1) / tile;
+    if (blocks > 0x7fffffff) return set_error(DPB_ERR_VALUE, "fused program: too many elements for one launch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (prog->typenum == DPB_DOUBLE) {
+        DPB_CUDA_TRY(cudaFuncSetAttribute(ew_fused_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ew_fused_kernel<double><<<static_cast<int>(blocks), kFusedThreads, smem, s>>>(prm, n);
+    }
+    else {
+        DPB_CUDA_TRY(cudaFuncSetAttribute(ew_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ew_fused_kernel<float><<<static_cast<int>(blocks), kFusedThreads, smem, s>>>(prm, n);
+    }
+    note_kernel("ew_fused");
+    return check_launch("ew_fused");
+}

@@ -138,7 +138,9 @@ __global__ void __launch_bounds__(kEwThreads)
 // The innermost collapsed dimension (length L) has stride 0 or 1 in every
 // operand; `outer` describes the remaining dimensions.  A block is TX threads
 // along the row times TY rows; a work item is (row group, chunk of the row).
-template <class F, int VEC, int UNROLL>
+// IB >= 0: the broadcast mask of the innermost dimension is the compile-time value IB, so a
+// chunk that lies wholly inside the row issues all its loads before the first use.
+template <class F, int VEC, int UNROLL, int IB>
 __global__ void __launch_bounds__(kEwThreads, 5)
     ew_rows_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> outer, int64_t L, unsigned inner_bcast,
                    int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div,
@@ -209,6 +211,39 @@ __global__ void __launch_bounds__(kEwThreads, 5)
         const int64_t Lb = L - head;
 
         const int64_t v0 = chunk * (int64_t(TX) * UNROLL) + tx;  // first vector index
+        if constexpr (IB >= 0) {
+            constexpr bool S0 = F::NIN >= 1 && !(IB & 1), S1 = F::NIN >= 2 && !(IB & 2),
+                           S2 = F::NIN >= 3 && !(IB & 4);
+            if ((chunk + 1) * (int64_t(TX) * UNROLL) * VEC <= Lb) {
+                vec_t<In0, VEC> va[S0 ? UNROLL : 1];
+                vec_t<In1, VEC> vb[S1 ? UNROLL : 1];
+                vec_t<In2, VEC> vc[S2 ? UNROLL : 1];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int64_t j = (v0 + int64_t(u) * TX) * VEC;
+                    if constexpr (S0) va[u] = load_vec<vec_t<In0, VEC>>(a + j);
+                    if constexpr (S1) vb[u] = load_vec<vec_t<In1, VEC>>(b + j);
+                    if constexpr (S2) vc[u] = load_vec<vec_t<In2, VEC>>(c + j);
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int64_t j = (v0 + int64_t(u) * TX) * VEC;
+                    vec_t<Out, VEC> r;
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) {
+                        In0 x = sa;
+                        In1 y = sb;
+                        In2 z = sc;
+                        if constexpr (S0) x = va[u].v[k];
+                        if constexpr (S1) y = vb[u].v[k];
+                        if constexpr (S2) z = vc[u].v[k];
+                        r.v[k] = ew_apply(f, x, y, z);
+                    }
+                    store_vec(o + j, r);
+                }
+                continue;
+            }
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int64_t j = (v0 + int64_t(u) * TX) * VEC;  // first element
@@ -671,7 +706,9 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         auto misalign = [](const void *ptr, size_t elem) {
             return static_cast<int>((reinterpret_cast<uintptr_t>(ptr) / elem) % VEC);
         };
-        bool aligned = VEC > 1;
+        // vector accesses for the broadcast patterns that occur in practice (none; one of two
+        // inputs a single value per row); anything else goes element by element
+        bool aligned = VEC > 1 && (inner_bcast == 0 || (NIN == 2 && inner_bcast < 3));
         const int mis = misalign(out, sizeof(Out));
         for (int i = 0; i < last; ++i) aligned = aligned && (plan.strides[NARR - 1][i] % VEC == 0);
         for (int k = 0; k < NIN; ++k) {
@@ -689,16 +726,20 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         const int64_t chunks = ceil_div(nvec, int64_t(TX) * UNROLL);
         const int64_t nwork = ceil_div(nrows, TY) * chunks;
         const FastDiv32 chunk_div(static_cast<uint32_t>(chunks < (int64_t(1) << 31) ? chunks : 1));
+#define DPB_ROWS_LAUNCH(V, MASK)                                                                    \
+    ew_rows_kernel<F, V, UNROLL, MASK><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(              \
+        f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, head)
         if (vec > 1) {
-            ew_rows_kernel<F, VEC, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, head);
+            if (inner_bcast == 0) DPB_ROWS_LAUNCH(VEC, 0);
+            else if (inner_bcast == 1) DPB_ROWS_LAUNCH(VEC, (F::NIN == 2 ? 1 : 0));
+            else DPB_ROWS_LAUNCH(VEC, (F::NIN == 2 ? 2 : 0));
             note_kernel(head ? "ew_rows_vec_head" : "ew_rows_vec");
         }
         else {
-            ew_rows_kernel<F, 1, UNROLL><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(
-                f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, 0);
+            DPB_ROWS_LAUNCH(1, -1);
             note_kernel("ew_rows_scalar");
         }
+#undef DPB_ROWS_LAUNCH
         return check_launch("ew_rows");
     }
     case EW_TRANSPOSE: {

@@ -415,6 +415,80 @@ int dpb_search_over_axis(int op, const dpb_array *src, int trailing_dims_to_redu
 int dpb_black_scholes_f64(int64_t n, const double *price, const double *strike, const double *t,
                           double rate, double vol, double *call, double *put, void *stream);
 
+/* A fused elementwise chain as a register-machine program, evaluated per element by one
+ * kernel.  The reference evaluates such chains one ufunc launch at a time through
+ * DPNPUnaryFunc/DPNPBinaryFunc (dpnp/dpnp_algo/dpnp_elementwise_common.py:81-235,537-739);
+ * Python scalars become operands of the program instead of stride-0 arrays
+ * (dpnp/tensor/_elementwise_common.py:655-659).  Every operator is the one the per-op
+ * entry points use, so a program gives the bits of the op-by-op chain.
+ *
+ * All arrays are contiguous, hold `n` elements of the program's type (float32 or
+ * float64) and do not overlap; an input flagged in `in_is_scalar` holds one element that
+ * is broadcast.  Comparisons and logical operators give 1.0 / 0.0, SELECT tests != 0.
+ *
+ * Instruction word: op | dst << 8 | a << 16 | b << 24 | c << 32.  Operands a, b, c:
+ * 0..63 register, 64+i immediate i, 255 the result of the previous instruction.
+ * dst: a register, or 255 when only the next instruction reads the result.
+ * LOAD: a = input index.  STORE: a = operand, b = output index.  SELECT: a ? b : c. */
+typedef enum dpb_fused_op {
+    DPB_FUSED_LOAD = 0,
+    DPB_FUSED_STORE,
+    DPB_FUSED_SELECT,
+    DPB_FUSED_MOVE,
+    DPB_FUSED_POSITIVE,
+    DPB_FUSED_NEGATIVE,
+    DPB_FUSED_ABS,
+    DPB_FUSED_EXP,
+    DPB_FUSED_LOG,
+    DPB_FUSED_SQRT,
+    DPB_FUSED_ERF,
+    DPB_FUSED_SQUARE,
+    DPB_FUSED_RECIPROCAL,
+    DPB_FUSED_SIN,
+    DPB_FUSED_COS,
+    DPB_FUSED_TANH,
+    DPB_FUSED_EXPM1,
+    DPB_FUSED_LOG1P,
+    DPB_FUSED_FLOOR,
+    DPB_FUSED_CEIL,
+    DPB_FUSED_SIGN,
+    DPB_FUSED_FIRST_BINARY,
+    DPB_FUSED_ADD = DPB_FUSED_FIRST_BINARY,
+    DPB_FUSED_SUBTRACT,
+    DPB_FUSED_MULTIPLY,
+    DPB_FUSED_DIVIDE,
+    DPB_FUSED_MAXIMUM,
+    DPB_FUSED_MINIMUM,
+    DPB_FUSED_POW,
+    DPB_FUSED_LESS,
+    DPB_FUSED_LESS_EQUAL,
+    DPB_FUSED_GREATER,
+    DPB_FUSED_GREATER_EQUAL,
+    DPB_FUSED_EQUAL,
+    DPB_FUSED_NOT_EQUAL,
+    DPB_FUSED_LOGICAL_AND,
+    DPB_FUSED_LOGICAL_OR,
+    DPB_FUSED_OP_COUNT
+} dpb_fused_op;
+
+typedef struct dpb_fused_program {
+    int32_t typenum;             /* DPB_FLOAT or DPB_DOUBLE */
+    int32_t n_instr;             /* <= 192 */
+    int32_t n_reg;               /* registers the program uses, <= 24 */
+    int32_t n_imm;               /* <= 48 */
+    int32_t n_in;                /* <= 12 */
+    int32_t n_out;               /* <= 8 */
+    const uint64_t *code;        /* host memory, n_instr words */
+    const double *imm;           /* host memory; converted to the program's type */
+    const void *const *in;       /* device pointers */
+    const int32_t *in_is_scalar; /* may be NULL: no scalar inputs */
+    void *const *out;            /* device pointers */
+} dpb_fused_program;
+
+/* Runs the program over n elements with one launch.  DPB_ERR_VALUE for a malformed
+ * program (every index is checked on the host before the launch). */
+int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, void *stream);
+
 /* ------------------------------------------------------- device-side fill */
 /* Counter-based uniform generator: element i of the output depends only on
  * (seed, i), so any shard of an array can be produced independently.
