@@ -641,7 +641,8 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     return out
 
 
-PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "sum_axis1",
+PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "rows_bcast",
+                 "argmax_axis0", "sum_axis1",
                  "sum_axis0", "mean_all", "transpose_c4", "max_i32", "argmax_i32")
 
 
@@ -668,6 +669,18 @@ def profile_case(name, launches=3):
         S = C.c_void_p(q.stream)
         fn = lambda: _lib.lib.dpb_black_scholes_f64(n, p.get_array()._ptr, s.get_array()._ptr, t.get_array()._ptr,
                                                     RATE, VOL, c.get_array()._ptr, u.get_array()._ptr, S)
+    elif name == "bs_fuse":
+        n = 1 << 24
+        p, s, t = dp.random.uniform(10, 50, n), dp.random.uniform(10, 50, n), dp.random.uniform(1, 2, n)
+        c, u = dp.empty(n), dp.empty(n)
+        chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
+        fn = lambda: chain(p, s, t, c, u)
+    elif name == "rows_bcast":
+        x, r, o = dp.random.uniform(-1, 1, (8192, 4096)), dp.random.uniform(-1, 1, 4096), dp.empty((8192, 4096))
+        fn = lambda: dp.subtract(x, r, out=o)
+    elif name == "argmax_axis0":
+        x = dp.random.uniform(-1, 1, (64, 1024, 512))
+        fn = lambda: dp.argmax(x, axis=0)
     elif name in ("sum_axis1", "sum_axis0", "mean_all"):
         x = dp.random.normal(0, 1, (4096, 65536), dtype="f4")
         fn = {"sum_axis1": lambda: dp.sum(x, axis=1), "sum_axis0": lambda: dp.sum(x, axis=0),

@@ -13,17 +13,23 @@ import numpy as _np
 
 from . import _lib, memory, random, scipy, tensor
 from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
-                     asnumpy, astype, broadcast_to, check_limitations, copy, copyto,
+                     asnumpy, astype, broadcast_to, check_limitations, copy, copyto, count_nonzero,
                      default_float_type, empty, empty_like, expand_dims, flip, full, full_like,
                      get_result_array, get_usm_ndarray, get_usm_ndarray_or_scalar,
-                     is_supported_array_type, max, mean, min, ones, ones_like, prod, ravel, reshape,
-                     squeeze, sum, transpose, where, zeros, zeros_like)
+                     is_supported_array_type, logsumexp, max, mean, min, ones, ones_like, prod, ravel, reduce_hypot, reshape,
+                     squeeze, std, sum, transpose, var, where, zeros, zeros_like)
 from ._fusion import fuse
 from ._ufuncs import (DPNPBinaryFunc, DPNPUnaryFunc, abs, absolute, add, ceil, cos, divide, equal, erf,
                       exp, expm1, floor, greater, greater_equal, isfinite, isinf, isnan, less,
                       less_equal, log, log1p, logical_and, logical_not, logical_or, maximum, minimum,
                       multiply, negative, not_equal, positive, power, reciprocal, sign, sin, sqrt,
                       square, subtract, tanh, true_divide)
+from ._ufuncs import (acos, acosh, angle, arccos, arccosh, arcsin, arcsinh, arctan, arctan2, arctanh, asin,
+                      asinh, atan, atan2, atanh, bitwise_and, bitwise_invert, bitwise_left_shift,
+                      bitwise_not, bitwise_or, bitwise_right_shift, bitwise_xor, cbrt, conj, conjugate,
+                      copysign, cosh, exp2, fix, floor_divide, hypot, imag, invert, left_shift, log2,
+                      log10, logaddexp, logical_xor, mod, nextafter, proj, real, remainder, right_shift,
+                      rint, rsqrt, signbit, sinh, tan, trunc)
 from .dpnp_array import dpnp_array
 from .dpnp_array import dpnp_array as ndarray
 from .memory import ExecutionPlacementError, StreamQueue, get_default_queue

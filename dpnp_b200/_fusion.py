@@ -392,7 +392,13 @@ class _Program:
             elif k[0] == "un":
                 word = (_OPS[k[1]], opnd(k[2], p, regs), 0, 0)
             elif k[0] == "bin":
-                word = (_OPS[k[1]], opnd(k[2], p, regs), opnd(k[3], p, regs), 0)
+                oa, ob = opnd(k[2], p, regs), opnd(k[3], p, regs)
+                if ob == _OPND_ACC and oa != _OPND_ACC:
+                    # the interpreter computes in place on the accumulator: hand it the
+                    # accumulator first and flag that it is the operator's second operand
+                    word = (_OPS[k[1]] | 1 << 40, ob, oa, 0)
+                else:
+                    word = (_OPS[k[1]], oa, ob, 0)
             else:
                 word = (_OPS["select"], opnd(k[1], p, regs), opnd(k[2], p, regs), opnd(k[3], p, regs))
             # registers whose last reader is this instruction are free for its result
@@ -440,6 +446,8 @@ class _Program:
         out = []
         for w in self.code[:self.n_instr]:
             op, dst, a, b, c3 = w & 255, (w >> 8) & 255, (w >> 16) & 255, (w >> 24) & 255, (w >> 32) & 255
+            if (w >> 40) & 1:                          # accumulator-first encoding of op(b, a)
+                a, b = b, a
             out.append((names[op], dst, a, b, c3))
         return out
 

@@ -251,6 +251,55 @@ def mean(a, /, axis=None, dtype=None, out=None, keepdims=False, *, where=True):
     return get_result_array(res, out, casting="unsafe")
 
 
+def count_nonzero(a, axis=None, *, keepdims=False, out=None):
+    """Number of non-zero elements over `axis` (dpnp/dpnp_iface_counting.py:49-105)."""
+    return get_result_array(dpt.count_nonzero(get_usm_ndarray(a), axis=axis, keepdims=keepdims), out)
+
+
+def logsumexp(x, /, *, axis=None, out=None, dtype=None, keepdims=False):
+    """log(sum(exp(x))) over `axis` (dpnp/dpnp_iface_trigonometric.py: logsumexp)."""
+    res = dpt.logsumexp(get_usm_ndarray(x), axis=axis, dtype=dtype, keepdims=keepdims)
+    return get_result_array(res, out, casting="same_kind")
+
+
+def reduce_hypot(x, /, *, axis=None, out=None, dtype=None, keepdims=False):
+    """sqrt(sum(x**2)) over `axis` (dpnp/dpnp_iface_trigonometric.py: reduce_hypot)."""
+    res = dpt.reduce_hypot(get_usm_ndarray(x), axis=axis, dtype=dtype, keepdims=keepdims)
+    return get_result_array(res, out, casting="same_kind")
+
+
+def _spread(name, a, axis, dtype, out, ddof, keepdims, where, mean, correction):
+    """Shared keyword handling of var/std (dpnp/dpnp_iface_statistics.py:1470-1668 and
+    :1665-1860): `correction` is the array-API spelling of `ddof`; complex input and a
+    caller-supplied `mean` are outside this path."""
+    if not is_supported_array_type(a):
+        raise TypeError(f"An array must be any of supported type, but got {type(a)}")
+    check_limitations(where=where)
+    if correction is not None:
+        if ddof != 0:
+            raise ValueError("ddof and correction can't be provided simultaneously.")
+        ddof = correction
+    if not isinstance(ddof, (int, float)):
+        raise TypeError(f"An integer or float is required, but got {type(ddof)}")
+    if mean is not None:
+        raise NotImplementedError(f"{name} with a precomputed mean is not provided by this path")
+    fn = dpt.var if name == "var" else dpt.std
+    result = get_result_array(fn(get_usm_ndarray(a), axis=axis, correction=ddof, keepdims=keepdims), out)
+    if dtype is not None and out is None:
+        result = result.astype(dtype, casting="same_kind")
+    return result
+
+
+def var(a, /, axis=None, dtype=None, out=None, ddof=0, keepdims=False, *, where=True, mean=None,
+        correction=None):
+    return _spread("var", a, axis, dtype, out, ddof, keepdims, where, mean, correction)
+
+
+def std(a, /, axis=None, dtype=None, out=None, ddof=0, keepdims=False, *, where=True, mean=None,
+        correction=None):
+    return _spread("std", a, axis, dtype, out, ddof, keepdims, where, mean, correction)
+
+
 def where(condition, x=None, y=None, /, *, order="K", out=None):
     """Elements from `x` where `condition` holds, else from `y`
     (dpnp/dpnp_iface_searching.py:386-475; the one-argument form is not on this path)."""

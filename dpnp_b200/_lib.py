@@ -50,11 +50,15 @@ def supported_dtypes():
 UNARY_OPS = {name: i for i, name in enumerate([
     "negative", "positive", "abs", "exp", "log", "sqrt", "erf", "square", "reciprocal",
     "sin", "cos", "tanh", "expm1", "log1p", "floor", "ceil", "sign", "logical_not",
-    "isnan", "isfinite", "isinf"])}
+    "isnan", "isfinite", "isinf", "acos", "acosh", "asin", "asinh", "atan", "atanh", "cbrt", "cosh", "sinh",
+    "tan", "exp2", "log2", "log10", "rsqrt", "trunc", "round", "signbit", "bitwise_invert", "conj", "real",
+    "imag", "angle", "proj"])}
 BINARY_OPS = {name: i for i, name in enumerate([
     "add", "subtract", "multiply", "divide", "maximum", "minimum", "equal", "not_equal",
-    "less", "less_equal", "greater", "greater_equal", "logical_and", "logical_or", "pow"])}
-REDUCE_OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+    "less", "less_equal", "greater", "greater_equal", "logical_and", "logical_or", "pow", "atan2", "hypot",
+    "copysign", "logaddexp", "nextafter", "bitwise_and", "bitwise_or", "bitwise_xor", "bitwise_left_shift",
+    "bitwise_right_shift", "floor_divide", "remainder", "logical_xor"])}
+REDUCE_OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "logsumexp": 4, "hypot": 5}
 SEARCH_OPS = {"argmax": 0, "argmin": 1}
 
 OK, ERR_VALUE, ERR_RUNTIME, ERR_CUDA, ERR_MEMORY, ERR_TYPE = range(6)

@@ -169,3 +169,42 @@ greater = DPNPBinaryFunc(ef.greater)
 greater_equal = DPNPBinaryFunc(ef.greater_equal)
 logical_and = DPNPBinaryFunc(ef.logical_and)
 logical_or = DPNPBinaryFunc(ef.logical_or)
+
+# the rest of the elementwise family, NumPy names (dpnp/dpnp_iface_trigonometric.py,
+# dpnp_iface_mathematical.py, dpnp_iface_bitwise.py, dpnp_iface_logic.py)
+acos = arccos = DPNPUnaryFunc(ef.acos, "acos")
+acosh = arccosh = DPNPUnaryFunc(ef.acosh, "acosh")
+asin = arcsin = DPNPUnaryFunc(ef.asin, "asin")
+asinh = arcsinh = DPNPUnaryFunc(ef.asinh, "asinh")
+atan = arctan = DPNPUnaryFunc(ef.atan, "atan")
+atanh = arctanh = DPNPUnaryFunc(ef.atanh, "atanh")
+cbrt = DPNPUnaryFunc(ef.cbrt)
+cosh = DPNPUnaryFunc(ef.cosh)
+sinh = DPNPUnaryFunc(ef.sinh)
+tan = DPNPUnaryFunc(ef.tan)
+exp2 = DPNPUnaryFunc(ef.exp2)
+log2 = DPNPUnaryFunc(ef.log2)
+log10 = DPNPUnaryFunc(ef.log10)
+rsqrt = DPNPUnaryFunc(ef.rsqrt)
+trunc = fix = DPNPUnaryFunc(ef.trunc)
+rint = DPNPUnaryFunc(ef.round, "rint")
+signbit = DPNPUnaryFunc(ef.signbit)
+invert = bitwise_not = bitwise_invert = DPNPUnaryFunc(ef.bitwise_invert, "invert")
+conj = conjugate = DPNPUnaryFunc(ef.conj, "conjugate")
+real = DPNPUnaryFunc(ef.real)
+imag = DPNPUnaryFunc(ef.imag)
+angle = DPNPUnaryFunc(ef.angle)
+proj = DPNPUnaryFunc(ef.proj)
+atan2 = arctan2 = DPNPBinaryFunc(ef.atan2, "atan2")
+hypot = DPNPBinaryFunc(ef.hypot)
+copysign = DPNPBinaryFunc(ef.copysign)
+logaddexp = DPNPBinaryFunc(ef.logaddexp)
+nextafter = DPNPBinaryFunc(ef.nextafter)
+bitwise_and = DPNPBinaryFunc(ef.bitwise_and)
+bitwise_or = DPNPBinaryFunc(ef.bitwise_or)
+bitwise_xor = DPNPBinaryFunc(ef.bitwise_xor)
+left_shift = bitwise_left_shift = DPNPBinaryFunc(ef.bitwise_left_shift, "left_shift")
+right_shift = bitwise_right_shift = DPNPBinaryFunc(ef.bitwise_right_shift, "right_shift")
+floor_divide = DPNPBinaryFunc(ef.floor_divide)
+remainder = mod = DPNPBinaryFunc(ef.remainder)
+logical_xor = DPNPBinaryFunc(ef.logical_xor)

@@ -47,6 +47,7 @@ struct DeviceProps {
 };
 const DeviceProps &device_props();
 int64_t tuning_ctas_per_sm();
+int64_t tuning_fused_elems();  // elements per thread and register of the fused-chain interpreter
 
 // ------------------------------------------------------------ element types
 

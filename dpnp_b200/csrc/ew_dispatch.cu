@@ -26,6 +26,11 @@ const EwTables &ew_tables()
         register_binary_misc(g_tables);
         register_binary_cmp_a(g_tables);
         register_binary_cmp_b(g_tables);
+        register_unary_math2(g_tables);
+        register_unary_misc2(g_tables);
+        register_binary_fp2(g_tables);
+        register_binary_bits(g_tables);
+        register_binary_divmod(g_tables);
         register_where(g_tables);
         register_cast_a(g_tables);
         register_cast_b(g_tables);

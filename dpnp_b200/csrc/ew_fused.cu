@@ -10,7 +10,7 @@
 //
 // Execution model: a block owns a tile of kFusedThreads * K consecutive elements.  A thread
 // holds K elements of every virtual register in shared memory, laid out
-// [register][k][thread] (bank-conflict free), plus one "accumulator" -- the result of
+// [register][16-byte group][thread] (bank-conflict free), plus one "accumulator" -- the result of
 // the previous instruction -- in real registers, so that chains of dependent operations
 // do not bounce through shared memory.  Every thread of the grid executes the same
 // instruction stream: branches on the opcode are uniform.
@@ -23,7 +23,6 @@
 namespace dpb {
 
 constexpr int kFusedThreads = 128;
-constexpr int kFusedK = 8;             // elements per thread and register
 constexpr int kFusedMaxInstr = 192;
 constexpr int kFusedMaxImm = 48;
 constexpr int kFusedMaxIn = 12;
@@ -38,7 +37,7 @@ constexpr unsigned kNoDst = 255;       // result stays in the accumulator only
 struct FusedParams {
     int32_t n_instr;
     int32_t vector_io;                  // every array pointer is 16-byte aligned
-    uint64_t code[kFusedMaxInstr];      // op | dst << 8 | a << 16 | b << 24 | c << 32
+    uint64_t code[kFusedMaxInstr];      // op | dst << 8 | a << 16 | b << 24 | c << 32 | swap << 40
     double imm[kFusedMaxImm];
     const void *in[kFusedMaxIn];
     int32_t in_scalar[kFusedMaxIn];     // input is one element, broadcast
@@ -48,16 +47,21 @@ struct FusedParams {
 template <class T> DPB_D T as_flag(bool_t b) { return b.v ? T(1) : T(0); }
 
 // One decode per instruction: the opcode selects a loop over the thread's K elements.
+// The first operand is in `acc`, the result replaces it.
 #define DPB_FUSED_UN(CODE, EXPR)                                   \
     case CODE:                                                     \
-        _Pragma("unroll") for (int k = 0; k < K; ++k) { const T x = a[k]; r[k] = (EXPR); } \
+        _Pragma("unroll") for (int k = 0; k < K; ++k) { const T x = acc[k]; acc[k] = (EXPR); } \
         break;
 #define DPB_FUSED_BIN(CODE, EXPR)                                  \
     case CODE:                                                     \
-        _Pragma("unroll") for (int k = 0; k < K; ++k) { const T x = a[k]; const T y = b[k]; r[k] = (EXPR); } \
+        _Pragma("unroll") for (int k = 0; k < K; ++k) {            \
+            const T x = SWAP ? b[k] : acc[k];                      \
+            const T y = SWAP ? acc[k] : b[k];                      \
+            acc[k] = (EXPR);                                       \
+        }                                                          \
         break;
 
-template <class T, int K> DPB_D void fused_unary(int op, const T (&a)[K], T (&r)[K])
+template <class T, int K> DPB_D void fused_unary(int op, T (&acc)[K])
 {
     switch (op) {
         DPB_FUSED_UN(DPB_FUSED_NEGATIVE, NegativeOp<T>::apply(x))
@@ -76,13 +80,13 @@ template <class T, int K> DPB_D void fused_unary(int op, const T (&a)[K], T (&r)
         DPB_FUSED_UN(DPB_FUSED_FLOOR, FloorOp<T>::apply(x))
         DPB_FUSED_UN(DPB_FUSED_CEIL, CeilOp<T>::apply(x))
         DPB_FUSED_UN(DPB_FUSED_SIGN, SignOp<T>::apply(x))
-    default:  // DPB_FUSED_POSITIVE, DPB_FUSED_MOVE
-#pragma unroll
-        for (int k = 0; k < K; ++k) r[k] = a[k];
+    default:  // DPB_FUSED_POSITIVE, DPB_FUSED_MOVE: the value itself
+        break;
     }
 }
 
-template <class T, int K> DPB_D void fused_binary(int op, const T (&a)[K], const T (&b)[K], T (&r)[K])
+// SWAP: the accumulator holds the SECOND operand of the operator.
+template <class T, int K, bool SWAP> DPB_D void fused_binary(int op, T (&acc)[K], const T (&b)[K])
 {
     switch (op) {
         DPB_FUSED_BIN(DPB_FUSED_ADD, (AddOp<T, T>::apply(x, y)))
@@ -101,21 +105,24 @@ template <class T, int K> DPB_D void fused_binary(int op, const T (&a)[K], const
         DPB_FUSED_BIN(DPB_FUSED_LOGICAL_AND, ((x != T(0) && y != T(0)) ? T(1) : T(0)))
         DPB_FUSED_BIN(DPB_FUSED_LOGICAL_OR, ((x != T(0) || y != T(0)) ? T(1) : T(0)))
     default:
-#pragma unroll
-        for (int k = 0; k < K; ++k) r[k] = a[k];
+        break;
     }
 }
 #undef DPB_FUSED_UN
 #undef DPB_FUSED_BIN
 
-template <class T>
+// K: elements per thread and register
+template <class T, int K>
 __global__ void __launch_bounds__(kFusedThreads)
     ew_fused_kernel(const __grid_constant__ FusedParams prm, int64_t n)
 {
-    constexpr int K = kFusedK;
     constexpr int VW = 16 / sizeof(T);  // elements per 16-byte access
+    constexpr int NV = K / VW;          // 16-byte groups per thread and register
+    using V = vec_t<T, VW>;
     extern __shared__ __align__(16) unsigned char fused_smem[];
-    T *regs = reinterpret_cast<T *>(fused_smem);
+    // register file: [register][group][thread] of 16-byte groups -- consecutive threads touch
+    // consecutive groups, so the 128-bit accesses are conflict-free
+    V *regs = reinterpret_cast<V *>(fused_smem);
     const int tid = threadIdx.x;
     const int64_t base = (int64_t(blockIdx.x) * kFusedThreads + tid) * K;  // first element of the thread
     if (base >= n) return;  // no block-wide barrier below: every thread works on its own slots
@@ -125,6 +132,7 @@ __global__ void __launch_bounds__(kFusedThreads)
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = T(0);
 
+    // operand -> v (the accumulator is copied; used where the value must outlive `acc`)
     auto fetch = [&](unsigned x, T(&v)[K]) {
         if (x == kOpndAcc) {
 #pragma unroll
@@ -137,7 +145,11 @@ __global__ void __launch_bounds__(kFusedThreads)
         }
         else {
 #pragma unroll
-            for (int k = 0; k < K; ++k) v[k] = regs[(x * K + k) * kFusedThreads + tid];
+            for (int g = 0; g < NV; ++g) {
+                const V t = regs[(x * NV + g) * kFusedThreads + tid];
+#pragma unroll
+                for (int j = 0; j < VW; ++j) v[g * VW + j] = t.v[j];
+            }
         }
     };
 
@@ -148,35 +160,35 @@ __global__ void __launch_bounds__(kFusedThreads)
         const unsigned oa = static_cast<unsigned>((w >> 16) & 0xff);
         const unsigned ob = static_cast<unsigned>((w >> 24) & 0xff);
         const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
-        T r[K];
+        const bool swap = (w >> 40) & 1;
         if (op == DPB_FUSED_LOAD) {
             const T *src = static_cast<const T *>(prm.in[oa]);
             if (prm.in_scalar[oa]) {
                 const T c = src[0];
 #pragma unroll
-                for (int k = 0; k < K; ++k) r[k] = c;
+                for (int k = 0; k < K; ++k) acc[k] = c;
             }
             else if (whole && prm.vector_io) {
 #pragma unroll
                 for (int k = 0; k < K; k += VW) {
-                    vec_t<T, VW> x = load_vec<vec_t<T, VW>>(src + base + k);
+                    V x = load_vec<V>(src + base + k);
 #pragma unroll
-                    for (int j = 0; j < VW; ++j) r[k + j] = x.v[j];
+                    for (int j = 0; j < VW; ++j) acc[k + j] = x.v[j];
                 }
             }
             else {
 #pragma unroll
-                for (int k = 0; k < K; ++k) r[k] = (base + k < n) ? src[base + k] : T(0);
+                for (int k = 0; k < K; ++k) acc[k] = (base + k < n) ? src[base + k] : T(0);
             }
         }
         else if (op == DPB_FUSED_STORE) {
+            T *dstp = static_cast<T *>(prm.out[ob]);
             T v[K];
             fetch(oa, v);
-            T *dstp = static_cast<T *>(prm.out[ob]);
             if (whole && prm.vector_io) {
 #pragma unroll
                 for (int k = 0; k < K; k += VW) {
-                    vec_t<T, VW> x;
+                    V x;
 #pragma unroll
                     for (int j = 0; j < VW; ++j) x.v[j] = v[k + j];
                     store_vec(dstp + base + k, x);
@@ -195,24 +207,29 @@ __global__ void __launch_bounds__(kFusedThreads)
             fetch(ob, a);
             fetch(oc, b);
 #pragma unroll
-            for (int k = 0; k < K; ++k) r[k] = (c[k] != T(0)) ? a[k] : b[k];
+            for (int k = 0; k < K; ++k) acc[k] = (c[k] != T(0)) ? a[k] : b[k];
         }
         else if (op < DPB_FUSED_FIRST_BINARY) {
-            T a[K];
-            fetch(oa, a);
-            fused_unary<T, K>(op, a, r);
+            if (oa != kOpndAcc) fetch(oa, acc);
+            fused_unary<T, K>(op, acc);
         }
         else {
-            T a[K], b[K];
-            fetch(oa, a);
+            // the accumulator takes the first operand (or already holds it); a second operand
+            // that is the accumulator is saved first
+            T b[K];
             fetch(ob, b);
-            fused_binary<T, K>(op, a, b, r);
+            if (oa != kOpndAcc) fetch(oa, acc);
+            if (swap) fused_binary<T, K, true>(op, acc, b);
+            else fused_binary<T, K, false>(op, acc, b);
         }
-#pragma unroll
-        for (int k = 0; k < K; ++k) acc[k] = r[k];
         if (dst != kNoDst) {
 #pragma unroll
-            for (int k = 0; k < K; ++k) regs[(dst * K + k) * kFusedThreads + tid] = r[k];
+            for (int g = 0; g < NV; ++g) {
+                V t;
+#pragma unroll
+                for (int j = 0; j < VW; ++j) t.v[j] = acc[g * VW + j];
+                regs[(dst * NV + g) * kFusedThreads + tid] = t;
+            }
         }
     }
 }
@@ -284,21 +301,29 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
     }
     if (n == 0 || prog->n_instr == 0) return DPB_OK;
     const size_t elem = prog->typenum == DPB_DOUBLE ? 8 : 4;
-    const size_t smem = static_cast<size_t>(prog->n_reg > 0 ? prog->n_reg : 1) * kFusedK * kFusedThreads * elem;
-    const int64_t tile = int64_t(kFusedThreads) * kFusedK;
+    const int K = static_cast<int>(tuning_fused_elems());
+    const size_t smem = static_cast<size_t>(prog->n_reg > 0 ? prog->n_reg : 1) * K * kFusedThreads * elem;
+    if (smem > device_props().max_smem_optin)
+        return set_error(DPB_ERR_VALUE, "fused program: %d registers do not fit in shared memory", prog->n_reg);
+    const int64_t tile = int64_t(kFusedThreads) * K;
     const int64_t blocks = (n + tile - 1) / tile;
     if (blocks > 0x7fffffff) return set_error(DPB_ERR_VALUE, "fused program: too many elements for one launch");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define DPB_FUSED_LAUNCH(T, KK)                                                                              \
+    do {                                                                                                     \
+        DPB_CUDA_TRY(cudaFuncSetAttribute(ew_fused_kernel<T, KK>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                          static_cast<int>(smem)));                                          \
+        ew_fused_kernel<T, KK><<<static_cast<int>(blocks), kFusedThreads, smem, s>>>(prm, n);                \
+    } while (0)
     if (prog->typenum == DPB_DOUBLE) {
-        DPB_CUDA_TRY(cudaFuncSetAttribute(ew_fused_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-        ew_fused_kernel<double><<<static_cast<int>(blocks), kFusedThreads, smem, s>>>(prm, n);
+        if (K == 8) DPB_FUSED_LAUNCH(double, 8);
+        else DPB_FUSED_LAUNCH(double, 4);
     }
     else {
-        DPB_CUDA_TRY(cudaFuncSetAttribute(ew_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-        ew_fused_kernel<float><<<static_cast<int>(blocks), kFusedThreads, smem, s>>>(prm, n);
+        if (K == 8) DPB_FUSED_LAUNCH(float, 8);
+        else DPB_FUSED_LAUNCH(float, 4);
     }
+#undef DPB_FUSED_LAUNCH
     note_kernel("ew_fused");
     return check_launch("ew_fused");
 }

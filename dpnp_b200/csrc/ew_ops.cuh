@@ -349,4 +349,286 @@ template <class A, class B> struct PowOp {
     }
 };
 
+
+// ===================================================================== more unary
+// Floating-point functions of one argument; float16 is computed in float32.
+#define DPB_FP_UNARY2(NAME, EXPR_F, EXPR_D)                                      \
+    template <class T> struct NAME {                                             \
+        using R = std::conditional_t<is_fp_v<T>, T, NoType>;                     \
+        static DPB_D R apply(T v)                                                \
+        {                                                                        \
+            if constexpr (std::is_same_v<T, double>) { const double x = v; return (EXPR_D); } \
+            else if constexpr (std::is_same_v<T, float>) { const float x = v; return (EXPR_F); } \
+            else { const float x = __half2float(v); return __float2half(EXPR_F); } \
+        }                                                                        \
+    };
+
+DPB_FP_UNARY2(AcosOp, acosf(x), acos(x))        // acos.hpp
+DPB_FP_UNARY2(AcoshOp, acoshf(x), acosh(x))     // acosh.hpp
+DPB_FP_UNARY2(AsinOp, asinf(x), asin(x))        // asin.hpp
+DPB_FP_UNARY2(AsinhOp, asinhf(x), asinh(x))     // asinh.hpp
+DPB_FP_UNARY2(AtanOp, atanf(x), atan(x))        // atan.hpp
+DPB_FP_UNARY2(AtanhOp, atanhf(x), atanh(x))     // atanh.hpp
+DPB_FP_UNARY2(CbrtOp, cbrtf(x), cbrt(x))        // cbrt.hpp
+DPB_FP_UNARY2(CoshOp, coshf(x), cosh(x))        // cosh.hpp
+DPB_FP_UNARY2(SinhOp, sinhf(x), sinh(x))        // sinh.hpp
+DPB_FP_UNARY2(TanOp, tanf(x), tan(x))           // tan.hpp
+DPB_FP_UNARY2(Exp2Op, exp2f(x), exp2(x))        // exp2.hpp
+DPB_FP_UNARY2(Log2Op, log2f(x), log2(x))        // log2.hpp
+DPB_FP_UNARY2(Log10Op, log10f(x), log10(x))     // log10.hpp
+// rsqrt.hpp: reciprocal of the correctly rounded square root
+DPB_FP_UNARY2(RsqrtOp, 1.0f / sqrtf(x), 1.0 / sqrt(x))
+#undef DPB_FP_UNARY2
+
+// trunc.hpp / round.hpp (round half to even): identity on integers
+template <class T> struct TruncOp {
+    using R = std::conditional_t<is_cplx_v<T> || is_bool_v<T>, NoType, T>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_half_v<T>) return htrunc(x);
+        else if constexpr (std::is_floating_point_v<T>) return trunc(x);
+        else return x;
+    }
+};
+
+template <class T> struct RoundOp {
+    using R = std::conditional_t<is_bool_v<T>, NoType, T>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_cplx_v<T>) return T(rint(x.re), rint(x.im));
+        else if constexpr (is_half_v<T>) return hrint(x);
+        else if constexpr (std::is_floating_point_v<T>) return rint(x);
+        else return x;
+    }
+};
+
+// signbit.hpp: floating types only
+template <class T> struct SignbitOp {
+    using R = std::conditional_t<is_fp_v<T>, bool_t, NoType>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_half_v<T>) return bool_t((__half_as_ushort(x) & 0x8000u) != 0);
+        else return bool_t(signbit(x));
+    }
+};
+
+// bitwise_invert.hpp: logical not for bool, complement for integers
+template <class T> struct BitwiseInvertOp {
+    using R = std::conditional_t<is_bool_v<T> || is_int_v<T>, T, NoType>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_bool_v<T>) return bool_t(!x.v);
+        else return static_cast<T>(~x);
+    }
+};
+
+// conj.hpp (bool -> int8), real.hpp, imag.hpp (real types: the value itself / zero)
+template <class T> struct ConjOp {
+    using R = std::conditional_t<is_bool_v<T>, int8_t, T>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_bool_v<T>) return x.v ? int8_t(1) : int8_t(0);
+        else if constexpr (is_cplx_v<T>) return T(x.re, -x.im);
+        else return x;
+    }
+};
+
+template <class T> struct RealOp {
+    using R = real_of_t<T>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_cplx_v<T>) return x.re;
+        else return x;
+    }
+};
+
+template <class T> struct ImagOp {
+    using R = real_of_t<T>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_cplx_v<T>) return x.im;
+        else if constexpr (is_bool_v<T>) return bool_t(false);
+        else if constexpr (is_half_v<T>) return __float2half(0.0f);
+        else return T(0);
+    }
+};
+
+// angle.hpp, proj.hpp: complex types only
+template <class T> struct AngleOp {
+    using R = std::conditional_t<is_cplx_v<T>, real_of_t<T>, NoType>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_cplx_v<T>) return atan2(x.im, x.re);
+        else return R{};
+    }
+};
+
+template <class T> struct ProjOp {
+    using R = std::conditional_t<is_cplx_v<T>, T, NoType>;
+    static DPB_D R apply(T x)
+    {
+        if constexpr (is_cplx_v<T>) {
+            using F = real_of_t<T>;
+            if (isinf(x.re) || isinf(x.im)) return T(F(INFINITY), copysign(F(0), x.im));
+            return x;
+        }
+        else return R{};
+    }
+};
+
+// ==================================================================== more binary
+#define DPB_FP_BINARY(NAME, EXPR_F, EXPR_D)                                      \
+    template <class A, class B> struct NAME {                                    \
+        using R = std::conditional_t<std::is_same_v<A, B> && is_fp_v<A>, A, NoType>; \
+        static DPB_D R apply(A a, B b)                                           \
+        {                                                                        \
+            if constexpr (std::is_same_v<A, double>) { const double x = a, y = b; return (EXPR_D); } \
+            else if constexpr (std::is_same_v<A, float>) { const float x = a, y = b; return (EXPR_F); } \
+            else { const float x = __half2float(a), y = __half2float(b); return __float2half(EXPR_F); } \
+        }                                                                        \
+    };
+
+template <class F> DPB_D F logaddexp_impl(F x, F y)
+{
+    // utils/math_utils.hpp:131-147
+    if (x == y) return x + log(F(2));
+    const F d = x - y;
+    return d > F(0) ? x + log1p(exp(-d)) : (d <= F(0) ? y + log1p(exp(d)) : F(NAN));
+}
+
+DPB_FP_BINARY(Atan2Op, atan2f(x, y), atan2(x, y))               // atan2.hpp
+DPB_FP_BINARY(HypotOp, hypotf(x, y), hypot(x, y))               // hypot.hpp
+DPB_FP_BINARY(CopysignOp, copysignf(x, y), copysign(x, y))      // copysign.hpp
+DPB_FP_BINARY(LogaddexpOp, logaddexp_impl<float>(x, y), logaddexp_impl<double>(x, y))  // logaddexp.hpp
+#undef DPB_FP_BINARY
+
+// nextafter.hpp: float16 steps in its own format
+template <class A, class B> struct NextafterOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && is_fp_v<A>, A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        if constexpr (std::is_same_v<A, double>) return (a == b) ? b : nextafter(a, b);
+        else if constexpr (std::is_same_v<A, float>) return (a == b) ? b : nextafterf(a, b);
+        else {
+            const float x = __half2float(a), y = __half2float(b);
+            if (x != x || y != y) return __float2half(x + y);
+            if (x == y) return b;
+            unsigned short u = __half_as_ushort(a);
+            if (x == 0.0f) return __ushort_as_half(static_cast<unsigned short>((y < 0.0f ? 0x8000u : 0u) | 1u));
+            const bool away = (y > x) == (x > 0.0f);   // magnitude grows
+            u = static_cast<unsigned short>(away ? u + 1 : u - 1);
+            return __ushort_as_half(u);
+        }
+    }
+};
+
+// bitwise_and.hpp / bitwise_or.hpp / bitwise_xor.hpp: bool and integers, identical types
+enum BitKind { BIT_AND, BIT_OR, BIT_XOR };
+template <int K, class A, class B> struct BitwiseOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && (is_bool_v<A> || is_int_v<A>), A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        if constexpr (is_bool_v<A>) {
+            if constexpr (K == BIT_AND) return bool_t(a.v && b.v);
+            else if constexpr (K == BIT_OR) return bool_t(a.v || b.v);
+            else return bool_t(bool(a.v) != bool(b.v));
+        }
+        else {
+            if constexpr (K == BIT_AND) return static_cast<A>(a & b);
+            else if constexpr (K == BIT_OR) return static_cast<A>(a | b);
+            else return static_cast<A>(a ^ b);
+        }
+    }
+};
+template <class A, class B> using BitwiseAndOp = BitwiseOp<BIT_AND, A, B>;
+template <class A, class B> using BitwiseOrOp = BitwiseOp<BIT_OR, A, B>;
+template <class A, class B> using BitwiseXorOp = BitwiseOp<BIT_XOR, A, B>;
+
+// bitwise_left_shift.hpp:88-104 / bitwise_right_shift.hpp:87-105: a negative count or one of at
+// least the bit width gives 0 (right shift of a negative value: -1)
+template <class A, class B> struct LeftShiftOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && is_int_v<A>, A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        constexpr int bits = static_cast<int>(sizeof(A) * 8);
+        if constexpr (std::is_signed_v<B>) { if (b < B(0)) return A(0); }
+        if (static_cast<uint64_t>(b) >= static_cast<uint64_t>(bits)) return A(0);
+        using U = std::make_unsigned_t<A>;
+        return static_cast<A>(static_cast<U>(static_cast<U>(a) << static_cast<int>(b)));
+    }
+};
+
+template <class A, class B> struct RightShiftOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && is_int_v<A>, A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        constexpr int bits = static_cast<int>(sizeof(A) * 8);
+        if constexpr (std::is_signed_v<B>) { if (b < B(0)) return A(0); }
+        if (static_cast<uint64_t>(b) >= static_cast<uint64_t>(bits)) {
+            if constexpr (std::is_signed_v<A>) return a < A(0) ? A(-1) : A(0);
+            else return A(0);
+        }
+        return static_cast<A>(a >> static_cast<int>(b));
+    }
+};
+
+// floor_divide.hpp / remainder.hpp: integers (division by zero gives 0) and floating types,
+// results follow the sign of the divisor
+template <class A, class B> struct FloorDivideOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && (is_int_v<A> || is_fp_v<A>), A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        if constexpr (is_int_v<A>) {
+            if (b == B(0)) return A(0);
+            if constexpr (std::is_signed_v<A>) {
+                if (b == B(-1)) return static_cast<A>(A(0) - static_cast<std::make_unsigned_t<A>>(a));
+                const A q = static_cast<A>(a / b), m = static_cast<A>(a % b);
+                return static_cast<A>(q - ((m != 0 && ((m < 0) != (b < 0))) ? 1 : 0));
+            }
+            else return static_cast<A>(a / b);
+        }
+        else {
+            const auto x = up(a), y = up(b);
+            const auto q = x / y;
+            using C = decltype(q);
+            return down<A>(q == C(0) ? q : floor(q));
+        }
+    }
+};
+
+template <class A, class B> struct RemainderOp {
+    using R = std::conditional_t<std::is_same_v<A, B> && (is_int_v<A> || is_fp_v<A>), A, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        if constexpr (is_int_v<A>) {
+            if (b == B(0)) return A(0);
+            if constexpr (std::is_signed_v<A>) {
+                if (b == B(-1)) return A(0);
+                A m = static_cast<A>(a % b);
+                if (m != 0 && ((a < 0) != (b < 0))) m = static_cast<A>(m + b);
+                return m;
+            }
+            else return static_cast<A>(a % b);
+        }
+        else {
+            const auto x = up(a), y = up(b);
+            auto r = fmod(x, y);
+            using C = decltype(r);
+            if (r != C(0)) {
+                if ((y < C(0)) != (r < C(0))) r += y;
+            }
+            else r = copysign(C(0), y);
+            return down<A>(r);
+        }
+    }
+};
+
+template <class A, class B> struct LogicalXorOp {
+    using R = std::conditional_t<std::is_same_v<A, B>, bool_t, NoType>;
+    static DPB_D R apply(A a, B b)
+    {
+        return bool_t(static_cast<bool>(convert<bool_t>(a)) != static_cast<bool>(convert<bool_t>(b)));
+    }
+};
+
 }  // namespace dpb

@@ -38,6 +38,11 @@ void register_binary_arith(EwTables &t);
 void register_binary_misc(EwTables &t);
 void register_binary_cmp_a(EwTables &t);
 void register_binary_cmp_b(EwTables &t);
+void register_unary_math2(EwTables &t);
+void register_unary_misc2(EwTables &t);
+void register_binary_fp2(EwTables &t);
+void register_binary_bits(EwTables &t);
+void register_binary_divmod(EwTables &t);
 void register_where(EwTables &t);
 void register_cast_a(EwTables &t);
 void register_cast_b(EwTables &t);

@@ -19,6 +19,7 @@ const RedTables &red_tables()
         register_reduce_prod(g_red);
         register_reduce_minmax(g_red);
         register_reduce_search(g_red);
+        register_reduce_fp(g_red);
     });
     return g_red;
 }

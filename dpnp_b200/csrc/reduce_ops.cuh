@@ -92,6 +92,35 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ProdRed {
     static DPB_D Out finish(Acc a) { return convert<Out>(a); }
 };
 
+// ------------------------------------------------- logsumexp and hypot
+// Floating types only (source/reductions/logsumexp.cpp, reduce_hypot.cpp); the merge of two
+// accumulators is the elementwise logaddexp / hypot (include/utils/sycl_utils.hpp:574-640).
+template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct LogSumExpRed {
+    using In = TIn;
+    using Acc = TAcc;
+    using Out = TOut;
+    using Stage2 = LogSumExpRed<Acc, TOut, Acc>;
+    static constexpr bool kVectorStep = false;
+    static DPB_D Acc identity() { return -static_cast<Acc>(INFINITY); }
+    static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
+    static DPB_D Acc combine(Acc a, Acc b) { return logaddexp_impl<Acc>(a, b); }
+    static DPB_D Out finish(Acc a) { return convert<Out>(a); }
+};
+
+template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct HypotRed {
+    using In = TIn;
+    using Acc = TAcc;
+    using Out = TOut;
+    using Stage2 = HypotRed<Acc, TOut, Acc>;
+    static constexpr bool kVectorStep = false;
+    static DPB_D Acc identity() { return Acc(0); }
+    static DPB_D Acc load(In v, int64_t) { return convert<Acc>(v); }
+    static DPB_D Acc step(Acc a, In v, int64_t i) { return combine(a, load(v, i)); }
+    static DPB_D Acc combine(Acc a, Acc b) { return hypot(a, b); }
+    static DPB_D Out finish(Acc a) { return convert<Out>(a); }
+};
+
 // ------------------------------------------------------------ max and min
 template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ExtremeRed {
     using In = TIn;

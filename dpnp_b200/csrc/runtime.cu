@@ -70,6 +70,8 @@ const DeviceProps &device_props()
 
 static std::atomic<int64_t> g_ctas_per_sm{8};
 int64_t tuning_ctas_per_sm() { return g_ctas_per_sm.load(std::memory_order_relaxed); }
+static std::atomic<int64_t> g_fused_elems{8};
+int64_t tuning_fused_elems() { return g_fused_elems.load(std::memory_order_relaxed); }
 
 
 // ------------------------------------------------------------------- pool
@@ -116,6 +118,10 @@ int dpb_set_tuning(const char *key, int64_t value)
 {
     if (key && std::strcmp(key, "ctas_per_sm") == 0 && value >= 1 && value <= 64) {
         g_ctas_per_sm.store(value);
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "fused_elems_per_thread") == 0 && (value == 4 || value == 8)) {
+        g_fused_elems.store(value);
         return DPB_OK;
     }
     return set_error(DPB_ERR_VALUE, "unknown tuning key or value out of range: %s",

@@ -215,9 +215,28 @@ class dpnp_array:
     def __ge__(self, o): return self._fn("greater_equal")(self, o)
     def __eq__(self, o): return self._fn("equal")(self, o)
     def __ne__(self, o): return self._fn("not_equal")(self, o)
-    def __and__(self, o): return self._fn("logical_and")(self, o)
-    def __or__(self, o): return self._fn("logical_or")(self, o)
-    def __invert__(self): return self._fn("logical_not")(self)
+    def __and__(self, o): return self._fn("bitwise_and")(self, o)
+    def __rand__(self, o): return self._fn("bitwise_and")(o, self)
+    def __iand__(self, o): self._fn("bitwise_and")(self, o, out=self); return self
+    def __or__(self, o): return self._fn("bitwise_or")(self, o)
+    def __ror__(self, o): return self._fn("bitwise_or")(o, self)
+    def __ior__(self, o): self._fn("bitwise_or")(self, o, out=self); return self
+    def __xor__(self, o): return self._fn("bitwise_xor")(self, o)
+    def __rxor__(self, o): return self._fn("bitwise_xor")(o, self)
+    def __ixor__(self, o): self._fn("bitwise_xor")(self, o, out=self); return self
+    def __invert__(self): return self._fn("invert")(self)
+    def __lshift__(self, o): return self._fn("left_shift")(self, o)
+    def __rlshift__(self, o): return self._fn("left_shift")(o, self)
+    def __ilshift__(self, o): self._fn("left_shift")(self, o, out=self); return self
+    def __rshift__(self, o): return self._fn("right_shift")(self, o)
+    def __rrshift__(self, o): return self._fn("right_shift")(o, self)
+    def __irshift__(self, o): self._fn("right_shift")(self, o, out=self); return self
+    def __floordiv__(self, o): return self._fn("floor_divide")(self, o)
+    def __rfloordiv__(self, o): return self._fn("floor_divide")(o, self)
+    def __ifloordiv__(self, o): self._fn("floor_divide")(self, o, out=self); return self
+    def __mod__(self, o): return self._fn("remainder")(self, o)
+    def __rmod__(self, o): return self._fn("remainder")(o, self)
+    def __imod__(self, o): self._fn("remainder")(self, o, out=self); return self
 
     __hash__ = None
 

@@ -15,9 +15,10 @@ from ._elementwise_funcs import (abs, add, ceil, cos, divide, equal, erf, exp, e
                                  square, subtract, tanh)
 from ._manipulation_functions import (broadcast_arrays, broadcast_shapes, broadcast_to, expand_dims,
                                       flip, permute_dims, reshape, squeeze)
-from ._reduction import all, any, argmax, argmin, max, min, prod, sum
+from ._reduction import (all, any, argmax, argmin, count_nonzero, logsumexp, max, min, prod, reduce_hypot,
+                         sum)
 from ._search_functions import where
-from ._statistical_functions import mean
+from ._statistical_functions import mean, std, var
 from ._type_utils import can_cast, result_type
 from ._usmarray import usm_ndarray
 

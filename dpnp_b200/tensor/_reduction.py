@@ -21,7 +21,7 @@ from ._copy_utils import _empty
 from ._ctors import empty_like
 from ._elementwise_common import _common_queue
 from ._manipulation_functions import normalize_axis_tuple, permute_dims, reshape, squeeze
-from ._type_utils import DEFAULT_INDEX, _default_accumulation_dtype
+from ._type_utils import DEFAULT_FP, DEFAULT_INDEX, _default_accumulation_dtype
 from ._usmarray import usm_ndarray
 
 
@@ -189,6 +189,55 @@ def prod(x, /, *, axis=None, dtype=None, keepdims=False, out=None):
     """Product of the elements over the given axes."""
     return _reduction_over_axis(x, axis, dtype, keepdims, out, tri._prod_over_axis,
                                 tri._prod_over_axis_dtype_supported, _default_accumulation_dtype)
+
+
+def _default_accumulation_dtype_fp_types(inp_dt):
+    """Result type of a reduction that exists for floating types only: the input's own type,
+    the default floating type for bool and integers (dpnp/tensor/_type_utils.py:955-972)."""
+    if inp_dt.kind in "biu":
+        res = DEFAULT_FP
+        return res if np.can_cast(inp_dt, res) else np.dtype("f8")
+    if inp_dt.kind == "f":
+        return inp_dt
+    raise ValueError("function not defined for complex types")
+
+
+def _to_fp_operand(x):
+    """bool and integer input of a floating-only reduction is converted to the result type first
+    (the reference's kernels convert each element on load: the values are the same)."""
+    if isinstance(x, usm_ndarray) and x.dtype.kind in "biu":
+        from ._copy_utils import astype
+        return astype(x, _default_accumulation_dtype_fp_types(x.dtype))
+    return x
+
+
+def logsumexp(x, /, *, axis=None, dtype=None, keepdims=False, out=None):
+    """log(sum(exp(x))) over the given axes, merged pairwise with logaddexp
+    (dpnp/tensor/_reduction.py:515-577)."""
+    x = _to_fp_operand(x)
+    return _reduction_over_axis(x, axis, dtype, keepdims, out, tri._logsumexp_over_axis,
+                                tri._logsumexp_over_axis_dtype_supported,
+                                _default_accumulation_dtype_fp_types)
+
+
+def reduce_hypot(x, /, *, axis=None, dtype=None, keepdims=False, out=None):
+    """sqrt(sum(x**2)) over the given axes, merged pairwise with hypot
+    (dpnp/tensor/_reduction.py:707-768)."""
+    x = _to_fp_operand(x)
+    return _reduction_over_axis(x, axis, dtype, keepdims, out, tri._hypot_over_axis,
+                                tri._hypot_over_axis_dtype_supported,
+                                _default_accumulation_dtype_fp_types)
+
+
+def count_nonzero(x, /, *, axis=None, keepdims=False, out=None):
+    """Number of non-zero elements: the sum of the truth values in the index type
+    (dpnp/tensor/_reduction.py:472-512)."""
+    if not isinstance(x, usm_ndarray):
+        raise TypeError(f"Expected dpnp.tensor.usm_ndarray, got {type(x)}")
+    if x.dtype != np.bool_:
+        from ._copy_utils import astype
+        x = astype(x, np.bool_, copy=False)
+    return sum(x, axis=axis, dtype=DEFAULT_INDEX, keepdims=keepdims, out=out)
 
 
 def max(x, /, *, axis=None, keepdims=False, out=None):

@@ -61,6 +61,21 @@ def _acceptance_fn_negative(arg_dtype, buf_dt, res_dt):
     return True
 
 
+def _acceptance_fn_reciprocal(arg_dtype, buf_dt, res_dt):
+    """When the input must change kind (an integer array), only the default floating type of
+    the result kind is accepted, which keeps reciprocal and divide aligned
+    (dpnp/tensor/_type_utils.py:122-133)."""
+    if buf_dt.kind != arg_dtype.kind:
+        return res_dt == _get_device_default_dtype(res_dt.kind)
+    return True
+
+
+def _acceptance_fn_round(arg_dtype, buf_dt, res_dt):
+    """Boolean input rounds to a floating result, not an integral one
+    (dpnp/tensor/_type_utils.py:136-140)."""
+    return not (arg_dtype.kind == "b" and res_dt.kind != "f")
+
+
 def _acceptance_fn_subtract(arg1_dtype, arg2_dtype, buf1_dt, buf2_dt, res_dt):
     if arg1_dtype.char == "?" and arg2_dtype.char == "?":
         raise ValueError(

@@ -456,8 +456,27 @@ class usm_ndarray:
     def __ge__(self, o): return self._ew("greater_equal")(self, o)
     def __eq__(self, o): return self._ew("equal")(self, o)
     def __ne__(self, o): return self._ew("not_equal")(self, o)
-    def __and__(self, o): return self._ew("logical_and")(self, o) if self._dtype.kind == "b" else NotImplemented
-    def __or__(self, o): return self._ew("logical_or")(self, o) if self._dtype.kind == "b" else NotImplemented
-    def __invert__(self): return self._ew("logical_not")(self) if self._dtype.kind == "b" else NotImplemented
+    def __and__(self, o): return self._ew("bitwise_and")(self, o)
+    def __rand__(self, o): return self._ew("bitwise_and")(o, self)
+    def __iand__(self, o): return self._ew("bitwise_and")._inplace_op(self, o)
+    def __or__(self, o): return self._ew("bitwise_or")(self, o)
+    def __ror__(self, o): return self._ew("bitwise_or")(o, self)
+    def __ior__(self, o): return self._ew("bitwise_or")._inplace_op(self, o)
+    def __xor__(self, o): return self._ew("bitwise_xor")(self, o)
+    def __rxor__(self, o): return self._ew("bitwise_xor")(o, self)
+    def __ixor__(self, o): return self._ew("bitwise_xor")._inplace_op(self, o)
+    def __invert__(self): return self._ew("bitwise_invert")(self)
+    def __lshift__(self, o): return self._ew("bitwise_left_shift")(self, o)
+    def __rlshift__(self, o): return self._ew("bitwise_left_shift")(o, self)
+    def __ilshift__(self, o): return self._ew("bitwise_left_shift")._inplace_op(self, o)
+    def __rshift__(self, o): return self._ew("bitwise_right_shift")(self, o)
+    def __rrshift__(self, o): return self._ew("bitwise_right_shift")(o, self)
+    def __irshift__(self, o): return self._ew("bitwise_right_shift")._inplace_op(self, o)
+    def __floordiv__(self, o): return self._ew("floor_divide")(self, o)
+    def __rfloordiv__(self, o): return self._ew("floor_divide")(o, self)
+    def __ifloordiv__(self, o): return self._ew("floor_divide")._inplace_op(self, o)
+    def __mod__(self, o): return self._ew("remainder")(self, o)
+    def __rmod__(self, o): return self._ew("remainder")(o, self)
+    def __imod__(self, o): return self._ew("remainder")._inplace_op(self, o)
 
     __hash__ = None

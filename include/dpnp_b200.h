@@ -115,6 +115,29 @@ typedef enum dpb_unary_op {
     DPB_U_ISNAN,        /* isnan.hpp */
     DPB_U_ISFINITE,     /* isfinite.hpp */
     DPB_U_ISINF,        /* isinf.hpp */
+    DPB_U_ACOS,         /* acos.hpp */
+    DPB_U_ACOSH,        /* acosh.hpp */
+    DPB_U_ASIN,         /* asin.hpp */
+    DPB_U_ASINH,        /* asinh.hpp */
+    DPB_U_ATAN,         /* atan.hpp */
+    DPB_U_ATANH,        /* atanh.hpp */
+    DPB_U_CBRT,         /* cbrt.hpp */
+    DPB_U_COSH,         /* cosh.hpp */
+    DPB_U_SINH,         /* sinh.hpp */
+    DPB_U_TAN,          /* tan.hpp */
+    DPB_U_EXP2,         /* exp2.hpp */
+    DPB_U_LOG2,         /* log2.hpp */
+    DPB_U_LOG10,        /* log10.hpp */
+    DPB_U_RSQRT,        /* rsqrt.hpp */
+    DPB_U_TRUNC,        /* trunc.hpp */
+    DPB_U_ROUND,        /* round.hpp:70-95 (half to even) */
+    DPB_U_SIGNBIT,      /* signbit.hpp */
+    DPB_U_BITWISE_INVERT, /* bitwise_invert.hpp */
+    DPB_U_CONJ,         /* conj.hpp */
+    DPB_U_REAL,         /* real.hpp */
+    DPB_U_IMAG,         /* imag.hpp */
+    DPB_U_ANGLE,        /* angle.hpp */
+    DPB_U_PROJ,         /* proj.hpp */
     DPB_U_NUM_OPS
 } dpb_unary_op;
 
@@ -135,6 +158,19 @@ typedef enum dpb_binary_op {
     DPB_B_LOGICAL_AND,   /* logical_and.hpp */
     DPB_B_LOGICAL_OR,    /* logical_or.hpp */
     DPB_B_POW,           /* pow.hpp */
+    DPB_B_ATAN2,         /* atan2.hpp */
+    DPB_B_HYPOT,         /* hypot.hpp */
+    DPB_B_COPYSIGN,      /* copysign.hpp */
+    DPB_B_LOGADDEXP,     /* logaddexp.hpp, utils/math_utils.hpp:131-147 */
+    DPB_B_NEXTAFTER,     /* nextafter.hpp */
+    DPB_B_BITWISE_AND,   /* bitwise_and.hpp */
+    DPB_B_BITWISE_OR,    /* bitwise_or.hpp */
+    DPB_B_BITWISE_XOR,   /* bitwise_xor.hpp */
+    DPB_B_BITWISE_LEFT_SHIFT,  /* bitwise_left_shift.hpp:88-104 */
+    DPB_B_BITWISE_RIGHT_SHIFT, /* bitwise_right_shift.hpp:87-105 */
+    DPB_B_FLOOR_DIVIDE,  /* floor_divide.hpp:67-90 */
+    DPB_B_REMAINDER,     /* remainder.hpp:66-100 */
+    DPB_B_LOGICAL_XOR,   /* logical_xor.hpp */
     DPB_B_NUM_OPS
 } dpb_binary_op;
 
@@ -144,6 +180,8 @@ typedef enum dpb_reduce_op {
     DPB_R_PROD,    /* source/reductions/prod.cpp */
     DPB_R_MAX,     /* source/reductions/max.cpp (NaN-propagating for fp) */
     DPB_R_MIN,     /* source/reductions/min.cpp */
+    DPB_R_LOGSUMEXP, /* source/reductions/logsumexp.cpp (floating types) */
+    DPB_R_HYPOT,   /* source/reductions/reduce_hypot.cpp (floating types) */
     DPB_R_NUM_OPS
 } dpb_reduce_op;
 
@@ -426,8 +464,10 @@ int dpb_black_scholes_f64(int64_t n, const double *price, const double *strike, 
  * float64) and do not overlap; an input flagged in `in_is_scalar` holds one element that
  * is broadcast.  Comparisons and logical operators give 1.0 / 0.0, SELECT tests != 0.
  *
- * Instruction word: op | dst << 8 | a << 16 | b << 24 | c << 32.  Operands a, b, c:
- * 0..63 register, 64+i immediate i, 255 the result of the previous instruction.
+ * Instruction word: op | dst << 8 | a << 16 | b << 24 | c << 32 | swap << 40.  Operands
+ * a, b, c: 0..63 register, 64+i immediate i, 255 the result of the previous instruction.
+ * A binary instruction computes op(a, b), or op(b, a) when swap is set (so that the
+ * previous result can always be given as a, where the interpreter works in place).
  * dst: a register, or 255 when only the next instruction reads the result.
  * LOAD: a = input index.  STORE: a = operand, b = output index.  SELECT: a ? b : c. */
 typedef enum dpb_fused_op {

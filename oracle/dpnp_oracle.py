@@ -70,9 +70,59 @@ def binary_result(op, x1, x2):
           "maximum": np.maximum, "minimum": np.minimum, "less": np.less, "less_equal": np.less_equal,
           "greater": np.greater, "greater_equal": np.greater_equal, "equal": np.equal,
           "not_equal": np.not_equal, "logical_and": np.logical_and, "logical_or": np.logical_or,
-          "power": np.power}[op]
+          "power": np.power, "atan2": np.arctan2, "hypot": np.hypot, "copysign": np.copysign,
+          "logaddexp": np.logaddexp, "nextafter": np.nextafter, "bitwise_and": np.bitwise_and,
+          "bitwise_or": np.bitwise_or, "bitwise_xor": np.bitwise_xor, "logical_xor": np.logical_xor,
+          "bitwise_left_shift": shift_left, "bitwise_right_shift": shift_right,
+          "floor_divide": floor_divide, "remainder": remainder}[op]
     with np.errstate(all="ignore"):
         return fn(x1, x2)
+
+
+def shift_left(x1, x2):
+    """include/kernels/elementwise_functions/bitwise_left_shift.hpp:88-104: a negative count or
+    one of at least the bit width gives 0."""
+    x1, x2 = np.asarray(x1), np.asarray(x2)
+    bits = x1.dtype.itemsize * 8
+    ok = (x2 >= 0) & (x2 < bits)
+    return np.where(ok, np.left_shift(x1, np.where(ok, x2, 0).astype(x1.dtype)), 0).astype(x1.dtype)
+
+
+def shift_right(x1, x2):
+    """bitwise_right_shift.hpp:87-105: as above, but a negative value shifted out entirely gives -1."""
+    x1, x2 = np.asarray(x1), np.asarray(x2)
+    bits = x1.dtype.itemsize * 8
+    ok = (x2 >= 0) & (x2 < bits)
+    over = np.where((x2 >= bits) & (x1 < 0), -1, 0) if x1.dtype.kind == "i" else 0
+    return np.where(ok, np.right_shift(x1, np.where(ok, x2, 0).astype(x1.dtype)), over).astype(x1.dtype)
+
+
+def floor_divide(x1, x2):
+    """floor_divide.hpp:67-90: integers floor towards minus infinity and give 0 for a zero
+    divisor; floating types give floor(x1 / x2), keeping a zero quotient as it is."""
+    x1, x2 = np.asarray(x1), np.asarray(x2)
+    with np.errstate(all="ignore"):
+        if x1.dtype.kind in "iu":
+            return np.where(x2 == 0, 0, np.floor_divide(x1, np.where(x2 == 0, 1, x2))).astype(x1.dtype)
+        ct = np.float32 if x1.dtype == np.float16 else x1.dtype.type
+        q = x1.astype(ct) / x2.astype(ct)
+        return np.where(q == 0, q, np.floor(q)).astype(x1.dtype)
+
+
+def remainder(x1, x2):
+    """remainder.hpp:66-100: the result takes the sign of the divisor; fmod-based for floats."""
+    x1, x2 = np.asarray(x1), np.asarray(x2)
+    with np.errstate(all="ignore"):
+        if x1.dtype.kind in "iu":
+            return np.where(x2 == 0, 0, np.remainder(x1, np.where(x2 == 0, 1, x2))).astype(x1.dtype)
+        ct = np.float32 if x1.dtype == np.float16 else x1.dtype.type
+        a, b = x1.astype(ct), x2.astype(ct)
+        r = np.fmod(a, b)
+        adj = (r != 0) & ((b < 0) != (r < 0))
+        r = np.where(adj, r + b, r)
+        r = np.where(r == 0, np.copysign(ct(0), b), r)
+        r = np.where(np.isnan(np.fmod(a, b)), np.fmod(a, b), r)
+        return r.astype(x1.dtype)
 
 
 def unary_result(op, x):
@@ -84,13 +134,33 @@ def unary_result(op, x):
         if x.dtype == np.float16:
             return sp.erf(x.astype(np.float32))
         return sp.erf(x)
+    if op in ("round", "trunc", "floor", "ceil") and x.dtype.kind in "iu":
+        return x.copy()                      # identity on integers (round.hpp:70-76, trunc.hpp)
     fn = {"exp": np.exp, "log": np.log, "sqrt": np.sqrt, "negative": np.negative, "abs": np.abs,
           "square": np.square, "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "expm1": np.expm1,
           "log1p": np.log1p, "floor": np.floor, "ceil": np.ceil, "sign": np.sign,
           "reciprocal": np.reciprocal, "positive": np.positive, "logical_not": np.logical_not,
-          "isnan": np.isnan, "isinf": np.isinf, "isfinite": np.isfinite}[op]
+          "isnan": np.isnan, "isinf": np.isinf, "isfinite": np.isfinite,
+          "acos": np.arccos, "acosh": np.arccosh, "asin": np.arcsin, "asinh": np.arcsinh,
+          "atan": np.arctan, "atanh": np.arctanh, "cbrt": np.cbrt, "cosh": np.cosh, "sinh": np.sinh,
+          "tan": np.tan, "exp2": np.exp2, "log2": np.log2, "log10": np.log10,
+          "rsqrt": lambda v: (1 / np.sqrt(v)).astype(v.dtype), "trunc": np.trunc, "round": np.rint,
+          "signbit": np.signbit, "bitwise_invert": np.invert, "conj": np.conj, "real": np.real,
+          "imag": np.imag, "angle": np.angle,
+          "proj": proj}[op]
     with np.errstate(all="ignore"):
         return fn(x)
+
+
+def proj(v):
+    """include/kernels/elementwise_functions/proj.hpp: infinite values (either part) map to
+    (inf, +-0 with the sign of the imaginary part), everything else is unchanged."""
+    v = np.asarray(v)
+    out = v.copy()
+    m = np.isinf(v.real) | np.isinf(v.imag)
+    out.real[m] = np.inf
+    out.imag[m] = np.copysign(0.0, v.imag[m])
+    return out
 
 
 def where(cond, x1, x2):

@@ -1,0 +1,211 @@
+"""The rest of the elementwise family (inverse trigonometric, hyperbolic, base-2/10, rounding,
+bit operations, floor division and remainder, complex parts) against the CPU oracle.
+
+Integer and bit results, rounding functions, copysign, nextafter, signbit and the complex-part
+functions are bit-exact.  Floating-point functions are compared with NumPy within 4 ulp (each
+side is within 2 ulp of the exact value)."""
+
+import zlib
+
+import numpy as np
+import pytest
+
+from oracle import dpnp_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+INTS = ["i1", "u1", "i2", "u2", "i4", "u4", "i8", "u8"]
+FLOATS = ["f2", "f4", "f8"]
+
+
+def dev(x):
+    import dpnp_b200 as dp
+
+    return dp.asarray(x)
+
+
+def ulps(got, ref):
+    got, ref = np.asarray(got), np.asarray(ref)
+    fin = np.isfinite(ref) & np.isfinite(got)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.array_equal(got[~fin & ~np.isnan(ref)], ref[~fin & ~np.isnan(ref)])
+    if not fin.any():
+        return 0.0
+    sp = np.spacing(np.abs(ref[fin]).astype(ref.dtype)).astype("f8")
+    return float(np.max(np.abs(got[fin].astype("f8") - ref[fin].astype("f8")) / sp))
+
+
+def assert_same_bits(got, ref, what=""):
+    """Bit equality, except that any NaN matches any NaN (the payload a NaN result carries is
+    not part of the contract)."""
+    got, ref = np.ascontiguousarray(got), np.ascontiguousarray(ref)
+    assert got.dtype == ref.dtype and got.shape == ref.shape, what
+    if got.dtype.kind == "c":
+        rt = got.real.dtype
+        got, ref = got.view(rt), ref.view(rt)
+    if got.dtype.kind == "f":
+        nan = np.isnan(ref)
+        assert np.array_equal(np.isnan(got), nan), what
+        got, ref = got[~nan], ref[~nan]
+    np.testing.assert_array_equal(got.view(np.uint8), ref.view(np.uint8), err_msg=what)
+
+
+DOMAINS = {"acos": (-1, 1), "asin": (-1, 1), "acosh": (1, 50), "atanh": (-0.999, 0.999), "log2": (1e-3, 1e3),
+           "log10": (1e-3, 1e3), "rsqrt": (1e-3, 1e3), "cosh": (-8, 8), "sinh": (-8, 8), "exp2": (-10, 10),
+           "tan": (-1.5, 1.5)}
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+@pytest.mark.parametrize("op", ["acos", "acosh", "asin", "asinh", "atan", "atanh", "cbrt", "cosh", "sinh", "tan",
+                                "exp2", "log2", "log10", "rsqrt"])
+def test_float_functions(op, dt):
+    import dpnp_b200 as dp
+
+    rng = np.random.default_rng(zlib.crc32(f"{op}{dt}".encode()))
+    lo, hi = DOMAINS.get(op, (-20, 20))
+    x = rng.uniform(lo, hi, 5000).astype(dt)
+    x[:4] = [np.nan, np.inf, -np.inf, 0.0]
+    got = getattr(dp.tensor._elementwise_funcs, op)(dev(x).get_array())
+    # float16 is evaluated in float32 and rounded once (NumPy's own float16 loops may use
+    # lower-accuracy vector routines, so they are not the reference here)
+    ref = orc.unary_result(op, x) if dt != "f2" else orc.unary_result(op, x.astype("f4")).astype("f2")
+    assert got.dtype == ref.dtype
+    limit = 4 if dt != "f2" else 1.01        # float16 is computed in float32 and rounded once
+    assert ulps(dp.asnumpy(got), ref) <= limit
+    # integers are promoted to the default floating type first
+    xi = rng.integers(1, 5, 100).astype("i4")
+    gi = getattr(dp, op if hasattr(dp, op) else "arc" + op[1:])(dev(xi))
+    with np.errstate(all="ignore"):
+        assert gi.dtype == np.dtype("f8") and ulps(gi.asnumpy(), orc.unary_result(op, xi.astype("f8"))) <= 4
+
+
+@pytest.mark.parametrize("dt", FLOATS + INTS + ["c8", "c16"])
+def test_rounding_sign_and_complex_parts_are_exact(dt):
+    import dpnp_b200 as dp
+    from dpnp_b200.tensor import _elementwise_funcs as ef
+
+    rng = np.random.default_rng(zlib.crc32(dt.encode()))
+    k = np.dtype(dt).kind
+    if k == "c":
+        x = (rng.uniform(-9, 9, 3000) + 1j * rng.uniform(-9, 9, 3000)).astype(dt)
+        x[:3] = [complex(np.inf, -1), complex(2, -np.inf), complex(np.nan, 0.0)]
+    elif k == "f":
+        x = (rng.integers(-40, 40, 3000) / 4).astype(dt)        # plenty of exact halves
+        x[:5] = [np.nan, np.inf, -np.inf, -0.0, 0.0]
+    else:
+        x = rng.integers(0 if k == "u" else -100, 100, 3000).astype(dt)
+    d = dev(x).get_array()
+    ops = ["round", "conj", "real", "imag"] + ([] if k == "c" else ["trunc"]) + (["signbit"] if k == "f" else []) \
+        + (["bitwise_invert"] if k in "iu" else []) + (["angle", "proj"] if k == "c" else [])
+    for op in ops:
+        got = dp.asnumpy(getattr(ef, op)(d))
+        ref = orc.unary_result(op, x)
+        assert got.dtype == ref.dtype, (op, got.dtype, ref.dtype)
+        if op == "angle":
+            assert ulps(got, ref) <= 4
+        else:
+            assert_same_bits(got, ref, op)
+    if k == "c":
+        assert ef.trunc.result_type_resolver_fn_(np.dtype(dt)) is None
+
+
+def test_bool_inputs_of_round_conj_and_invert():
+    import dpnp_b200 as dp
+    from dpnp_b200.tensor import _elementwise_funcs as ef
+
+    b = np.array([True, False, True])
+    d = dev(b).get_array()
+    assert dp.asnumpy(ef.conj(d)).dtype == np.dtype("i1")
+    np.testing.assert_array_equal(dp.asnumpy(ef.bitwise_invert(d)), ~b)
+    r = ef.round(d)                                   # bool rounds in a floating type
+    assert r.dtype.kind == "f"
+    np.testing.assert_array_equal(dp.asnumpy(r), b.astype(r.dtype))
+    np.testing.assert_array_equal((~dev(b)).asnumpy(), ~b)
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+def test_float_binary_functions(dt):
+    import dpnp_b200 as dp
+
+    rng = np.random.default_rng(zlib.crc32(dt.encode()) + 1)
+    x, y = rng.uniform(-30, 30, 4000).astype(dt), rng.uniform(-30, 30, 4000).astype(dt)
+    x[:6] = [np.nan, np.inf, -np.inf, 0.0, -0.0, 5.0]
+    y[:6] = [1.0, np.inf, np.inf, -0.0, 0.0, np.nan]
+    dx, dy = dev(x), dev(y)
+    for op in ("atan2", "hypot", "logaddexp"):
+        got = getattr(dp, op)(dx, dy).asnumpy()
+        ref = orc.binary_result(op, x, y) if dt != "f2" else \
+            orc.binary_result(op, x.astype("f4"), y.astype("f4")).astype("f2")
+        assert got.dtype == ref.dtype
+        assert ulps(got, ref) <= (4 if dt != "f2" else 1.01), op
+    for op in ("copysign", "nextafter"):
+        got = getattr(dp, op)(dx, dy).asnumpy()
+        ref = orc.binary_result(op, x, y)
+        if op == "nextafter":
+            ref = np.where(x == y, y, ref)             # equal operands give the second one (C rule)
+        assert_same_bits(got, ref, op)
+    for op, sym in (("floor_divide", "//"), ("remainder", "%")):
+        got = getattr(dp, op)(dx, dy).asnumpy()
+        ref = orc.binary_result(op, x, y)
+        nan = np.isnan(ref)
+        assert np.array_equal(np.isnan(got), nan), op
+        np.testing.assert_array_equal(got[~nan].view(np.uint8), ref[~nan].view(np.uint8), err_msg=op)
+    np.testing.assert_array_equal((dx[6:] // 3).asnumpy(), orc.floor_divide(x[6:], np.full_like(x[6:], 3)))
+    np.testing.assert_array_equal((dx[6:] % -7).asnumpy(), orc.remainder(x[6:], np.full_like(x[6:], -7)))
+
+
+@pytest.mark.parametrize("dt", INTS)
+def test_integer_binary_functions_are_exact(dt):
+    import dpnp_b200 as dp
+
+    rng = np.random.default_rng(zlib.crc32(dt.encode()) + 2)
+    info = np.iinfo(dt)
+    x = rng.integers(info.min, info.max, 4000, dtype=dt, endpoint=True)
+    y = rng.integers(info.min, info.max, 4000, dtype=dt, endpoint=True)
+    y[:4] = [0, 1, info.max, info.min]
+    x[:4] = [info.min, info.min, info.max, info.min]
+    if info.min < 0:
+        y[4], x[4] = -1, info.min                      # the one quotient that does not fit
+    dx, dy = dev(x), dev(y)
+    for op in ("bitwise_and", "bitwise_or", "bitwise_xor", "logical_xor"):
+        np.testing.assert_array_equal(getattr(dp, op)(dx, dy).asnumpy(), orc.binary_result(op, x, y), err_msg=op)
+    sel = np.ones(4000, bool)
+    if info.min < 0:
+        sel[4] = False                                 # NumPy's own answer for min // -1 is platform-defined
+    for op in ("floor_divide", "remainder"):
+        got = getattr(dp, op)(dx, dy).asnumpy()
+        np.testing.assert_array_equal(got[sel], orc.binary_result(op, x, y)[sel], err_msg=op)
+    if info.min < 0:
+        assert dp.floor_divide(dx, dy).asnumpy()[4] == info.min and dp.remainder(dx, dy).asnumpy()[4] == 0
+    bits = np.dtype(dt).itemsize * 8
+    s = rng.integers(-3 if info.min < 0 else 0, bits + 3, 4000).astype(dt)
+    ds = dev(s)
+    np.testing.assert_array_equal(dp.left_shift(dx, ds).asnumpy(), orc.shift_left(x, s))
+    np.testing.assert_array_equal(dp.right_shift(dx, ds).asnumpy(), orc.shift_right(x, s))
+    # operators, Python scalars, in-place forms
+    np.testing.assert_array_equal((dx & 7).asnumpy(), x & np.dtype(dt).type(7))
+    np.testing.assert_array_equal((dx ^ dy).asnumpy(), x ^ y)
+    np.testing.assert_array_equal((dx >> 2).asnumpy(), x >> np.dtype(dt).type(2))
+    np.testing.assert_array_equal((~dx).asnumpy(), ~x)
+    z = dev(x.copy())
+    z |= dy
+    np.testing.assert_array_equal(z.asnumpy(), x | y)
+    z = dev(x.copy())
+    z //= 3
+    np.testing.assert_array_equal(z.asnumpy(), x // np.dtype(dt).type(3))
+
+
+def test_type_rules_and_strided_operands():
+    import dpnp_b200 as dp
+
+    with pytest.raises((TypeError, ValueError)):
+        dp.bitwise_and(dev(np.ones(3)), dev(np.ones(3)))
+    # bool operands of a shift are promoted to int8, as every operand without an exact match is
+    assert dp.left_shift(dev(np.ones(3, "?")), dev(np.ones(3, "?"))).dtype == np.dtype("i1")
+    a = np.arange(-30, 30, dtype="i4").reshape(6, 10)
+    b = np.arange(1, 11, dtype="i2")
+    np.testing.assert_array_equal((dev(a).T % dev(b)[:6]).asnumpy(), a.T % b[:6].astype("i4"))
+    np.testing.assert_array_equal(dp.logical_xor(dev(a)[::2], dev(b)).asnumpy(), np.logical_xor(a[::2], b))
+    f = np.linspace(-4, 4, 60).reshape(6, 10)
+    got = dp.arctan2(dev(f)[:, ::-1], dev(f).T[:10, :6].T).asnumpy()
+    assert ulps(got, np.arctan2(f[:, ::-1], f)) <= 4
