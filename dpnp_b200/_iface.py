@@ -251,6 +251,50 @@ def mean(a, /, axis=None, dtype=None, out=None, keepdims=False, *, where=True):
     return get_result_array(res, out, casting="unsafe")
 
 
+def _cumulative(fn, a, axis, dtype, out, include_initial=False, flatten=True):
+    """cumsum/cumprod flatten a multi-dimensional input when no axis is given
+    (dpnp/dpnp_iface_mathematical.py:1100-1180); `out` of another type is filled by a cast
+    (dpnp/dpnp_utils/dpnp_utils_reduction.py:35-52)."""
+    if not is_supported_array_type(a):
+        raise TypeError(f"An array must be any of supported type, but got {type(a)}")
+    usm_a = get_usm_ndarray(a)
+    if flatten and usm_a.ndim > 1 and axis is None:
+        usm_a = dpt.reshape(usm_a, (-1,))
+    res_dt = np.dtype(dtype) if dtype is not None else None
+    usm_out = None
+    if out is not None:
+        if not is_supported_array_type(out):
+            raise TypeError(f"An array must be any of supported type, but got {type(out)}")
+        usm_out = get_usm_ndarray(out)
+        from .tensor._reduction import _default_accumulation_dtype_fp_types
+        default = _default_accumulation_dtype_fp_types if fn is dpt.cumulative_logsumexp \
+            else _default_accumulation_dtype
+        if usm_out.dtype != (res_dt if res_dt is not None else default(usm_a.dtype)):
+            usm_out = None                       # filled below by a cast
+    res = fn(usm_a, axis=axis, dtype=dtype, include_initial=include_initial, out=usm_out)
+    return get_result_array(res, out, casting="unsafe")
+
+
+def cumsum(a, axis=None, dtype=None, out=None):
+    return _cumulative(dpt.cumulative_sum, a, axis, dtype, out)
+
+
+def cumprod(a, axis=None, dtype=None, out=None):
+    return _cumulative(dpt.cumulative_prod, a, axis, dtype, out)
+
+
+def cumlogsumexp(x, /, *, axis=None, dtype=None, include_initial=False, out=None):
+    return _cumulative(dpt.cumulative_logsumexp, x, axis, dtype, out, include_initial, flatten=False)
+
+
+def cumulative_sum(x, /, *, axis=None, dtype=None, out=None, include_initial=False):
+    return _cumulative(dpt.cumulative_sum, x, axis, dtype, out, include_initial, flatten=False)
+
+
+def cumulative_prod(x, /, *, axis=None, dtype=None, out=None, include_initial=False):
+    return _cumulative(dpt.cumulative_prod, x, axis, dtype, out, include_initial, flatten=False)
+
+
 def count_nonzero(a, axis=None, *, keepdims=False, out=None):
     """Number of non-zero elements over `axis` (dpnp/dpnp_iface_counting.py:49-105)."""
     return get_result_array(dpt.count_nonzero(get_usm_ndarray(a), axis=axis, keepdims=keepdims), out)

@@ -60,6 +60,7 @@ BINARY_OPS = {name: i for i, name in enumerate([
     "bitwise_right_shift", "floor_divide", "remainder", "logical_xor"])}
 REDUCE_OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "logsumexp": 4, "hypot": 5}
 SEARCH_OPS = {"argmax": 0, "argmin": 1}
+ACCUMULATE_OPS = {"cumsum": 0, "cumprod": 1, "cumlogsumexp": 2}
 
 OK, ERR_VALUE, ERR_RUNTIME, ERR_CUDA, ERR_MEMORY, ERR_TYPE = range(6)
 
@@ -155,6 +156,8 @@ PROTOTYPES = {
     "dpb_search_over_axis": (_i, [_i, _parr, _i, _parr, _vp]),
     "dpb_black_scholes_f64": (_i, [_i64, _vp, _vp, _vp, _dbl, _dbl, _vp, _vp, _vp]),
     "dpb_fused_elementwise": (_i, [_vp, _i64, _vp]),
+    "dpb_accumulate_over_axis": (_i, [_i, _parr, _parr, _i, _vp]),
+    "dpb_accumulate_dtype_supported": (_i, [_i, _i, _i]),
     "dpb_random_uniform": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),
     "dpb_random_normal": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),
     "dpb_last_kernel": (C.c_char_p, []),

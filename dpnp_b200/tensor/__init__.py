@@ -18,6 +18,7 @@ from ._manipulation_functions import (broadcast_arrays, broadcast_shapes, broadc
 from ._reduction import (all, any, argmax, argmin, count_nonzero, logsumexp, max, min, prod, reduce_hypot,
                          sum)
 from ._search_functions import where
+from ._accumulation import cumulative_logsumexp, cumulative_prod, cumulative_sum
 from ._statistical_functions import mean, std, var
 from ._type_utils import can_cast, result_type
 from ._usmarray import usm_ndarray

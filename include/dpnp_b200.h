@@ -192,6 +192,14 @@ typedef enum dpb_search_op {
     DPB_S_NUM_OPS
 } dpb_search_op;
 
+/* Accumulations (prefix scans) along the last axis. */
+typedef enum dpb_accumulate_op {
+    DPB_A_CUMSUM = 0,     /* source/accumulators/cumulative_sum.cpp */
+    DPB_A_CUMPROD,        /* source/accumulators/cumulative_prod.cpp */
+    DPB_A_CUMLOGSUMEXP,   /* source/accumulators/cumulative_logsumexp.cpp (floating types) */
+    DPB_A_NUM_OPS
+} dpb_accumulate_op;
+
 /* -------------------------------------------------- errors and the device */
 
 /* Message of the last failure in the calling thread ("" if none). */
@@ -443,6 +451,19 @@ int dpb_reduction_over_axis(int op, const dpb_array *src, int trailing_dims_to_r
 /* Replaces py_search_over_axis (reduction_over_axis.hpp:780-1047). */
 int dpb_search_over_axis(int op, const dpb_array *src, int trailing_dims_to_reduce,
                          const dpb_array *dst, void *stream);
+
+/* Inclusive scan of `src` along its last axis into `dst` (same rank; same shape, or one more
+ * element along the last axis when include_initial is set: position 0 then holds the
+ * identity).  Any strides; src and dst may be the same array.  Replaces
+ * py_accumulate_over_axis and py_accumulate_final_axis_include_initial
+ * (dpnp/tensor/libtensor/source/accumulators/accumulate_over_axis.hpp:74-260,262-460) with
+ * trailing_dims_to_accumulate = 1, the only value the Python layer passes
+ * (dpnp/tensor/_accumulation.py:140-152). */
+int dpb_accumulate_over_axis(int op, const dpb_array *src, const dpb_array *dst, int include_initial,
+                             void *stream);
+/* 1 if (input type, output type) has a kernel for `op`, else 0
+ * (_cumsum_over_axis_dtype_supported etc.). */
+int dpb_accumulate_dtype_supported(int op, int t_in, int t_out);
 
 /* ------------------------------------------------- fused expression paths */
 /* Black-Scholes call/put for n options in one pass (3 loads, 2 stores per
