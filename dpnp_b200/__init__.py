@@ -15,9 +15,9 @@ from . import _lib, memory, random, scipy, tensor
 from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
                      asnumpy, astype, broadcast_to, check_limitations, copy, copyto, count_nonzero,
                      cumlogsumexp, cumprod, cumsum, cumulative_prod, cumulative_sum,
-                     default_float_type, empty, empty_like, expand_dims, flip, full, full_like,
+                     default_float_type, empty, empty_like, expand_dims, flip, from_dlpack, full, full_like,
                      get_result_array, get_usm_ndarray, get_usm_ndarray_or_scalar,
-                     is_supported_array_type, logsumexp, max, mean, min, ones, ones_like, prod, ravel, reduce_hypot, reshape,
+                     is_supported_array_type, linspace, logsumexp, max, mean, min, ones, ones_like, prod, ravel, reduce_hypot, reshape,
                      squeeze, std, sum, transpose, var, where, zeros, zeros_like)
 from ._fusion import fuse
 from ._ufuncs import (DPNPBinaryFunc, DPNPUnaryFunc, abs, absolute, add, ceil, cos, divide, equal, erf,

@@ -107,6 +107,22 @@ empty = _creation(dpt.empty)
 zeros = _creation(dpt.zeros)
 ones = _creation(dpt.ones)
 arange = _creation(dpt.arange)
+
+
+def linspace(start, stop, /, num, *, dtype=None, device=None, usm_type=None, sycl_queue=None, endpoint=True,
+             retstep=False, axis=0):
+    """Evenly spaced numbers over an interval (dpnp/dpnp_iface_arraycreation.py: linspace); scalar
+    end points only on this path."""
+    if retstep or axis != 0:
+        raise NotImplementedError("linspace with retstep or axis is not provided by this path")
+    return _wrap(dpt.linspace(start, stop, num, dtype=dtype, device=device, usm_type=usm_type or "device",
+                              sycl_queue=sycl_queue, endpoint=endpoint))
+
+
+def from_dlpack(x, /, *, device=None, copy=None):
+    """Array sharing the memory of a DLPack producer (dpnp/dpnp_iface.py: from_dlpack)."""
+    return _wrap(dpt.from_dlpack(x, device=device, copy=copy))
+
 empty_like = _creation(dpt.empty_like)
 zeros_like = _creation(dpt.zeros_like)
 ones_like = _creation(dpt.ones_like)

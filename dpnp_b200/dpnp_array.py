@@ -61,6 +61,12 @@ class dpnp_array:
         """The underlying :class:`usm_ndarray`."""
         return self._array_obj
 
+    def __dlpack__(self, **kwargs):
+        return self._array_obj.__dlpack__(**kwargs)
+
+    def __dlpack_device__(self):
+        return self._array_obj.__dlpack_device__()
+
     @property
     def __cuda_array_interface__(self):
         return self._array_obj.__cuda_array_interface__

@@ -6,8 +6,9 @@ import numpy as _np
 
 from ..memory import ExecutionPlacementError, StreamQueue, get_default_queue
 from ._copy_utils import asnumpy, astype, copy, from_numpy, to_numpy
-from ._ctors import (arange, asarray, empty, empty_like, full, full_like, ones, ones_like, zeros,
+from ._ctors import (arange, asarray, empty, empty_like, full, full_like, linspace, ones, ones_like, zeros,
                      zeros_like)
+from ._dlpack import from_dlpack
 from ._elementwise_funcs import (abs, add, ceil, cos, divide, equal, erf, exp, expm1, floor, greater,
                                  greater_equal, isfinite, isinf, isnan, less, less_equal, log, log1p,
                                  logical_and, logical_not, logical_or, maximum, minimum, multiply,

@@ -7,6 +7,7 @@ the stream-ordered pool, initial values from fill kernels or a host staging copy
 
 from __future__ import annotations
 
+import builtins
 import operator
 
 import numpy as np
@@ -160,9 +161,87 @@ def asarray(obj, /, *, dtype=None, device=None, copy=None, usm_type=None, sycl_q
     return from_numpy(np_ary, device=device, usm_type=usm_type or "device", sycl_queue=sycl_queue)
 
 
+def _get_arange_length(start, stop, step):
+    """Number of elements of arange: ceil((stop - start) / step), computed in Python numbers
+    (dpnp/tensor/_ctors.py:549-563)."""
+    span = stop - start
+    if type(step) in (int, float) and type(span) in (int, float):
+        import math
+        return math.ceil(span / step)
+    tmp = span / step
+    return tmp.real.__ceil__() if tmp.imag == 0 else min(tmp.real.__ceil__(), tmp.imag.__ceil__())
+
+
 def arange(start, /, stop=None, step=1, *, dtype=None, device=None, usm_type="device", sycl_queue=None):
-    """Evenly spaced values in a half-open interval (values computed on the host, one upload)."""
-    np_ary = np.arange(start, stop, step, dtype=dtype)
-    if dtype is None and np_ary.dtype.kind == "i":
-        np_ary = np_ary.astype(_default_int)
-    return from_numpy(np_ary, device=device, usm_type=usm_type, sycl_queue=sycl_queue)
+    """Evenly spaced values in a half-open interval, written on the device
+    (dpnp/tensor/_ctors.py:566-674): element i is ``first + i * (second - first)`` in the
+    array's own arithmetic, with first and second rounded to the array's type."""
+    if stop is None:
+        stop, start = start, 0
+    if step is None:
+        step = 1
+    _check_usm_type(usm_type)
+    for v in (start, stop, step):
+        if not isinstance(v, (int, float, np.integer, np.floating)) or isinstance(v, (bool, np.bool_)):
+            raise ValueError("start, stop, and step must be Python scalars")
+    q = normalize_queue(sycl_queue, device)
+    is_bool = dtype is not None and np.dtype(dtype) == np.bool_
+    if dtype is None:
+        dt = _default_fp if any(isinstance(v, (float, np.floating)) for v in (start, stop, step)) else _default_int
+    else:
+        dt = np.dtype("i1") if is_bool else np.dtype(dtype)
+    if dt.kind not in "iuf":
+        raise ValueError(f"arange does not produce arrays of type {dt}")
+    try:
+        sh = builtins.max(int(_get_arange_length(start, stop, step)), 0)
+    except (TypeError, ZeroDivisionError, OverflowError):
+        sh = 0
+    if is_bool and sh > 2:
+        raise ValueError("no fill-function for boolean data type")
+    res = _empty((sh,), dt, q, "C", usm_type)
+    if sh:
+        sc = dt.type
+        with np.errstate(all="ignore"):
+            first = sc(start)
+            if sh > 1:
+                second = sc(start + step)
+                stepv = sc(np.int64(second) - np.int64(first)) if dt.kind == "u" else sc(second - first)
+            else:
+                stepv = sc(1)
+        a0, a1 = np.array([first], dtype=dt), np.array([stepv], dtype=dt)
+        _lib.check(_lib.lib.dpb_linspace_step(_lib.typenum_of(dt), res._ptr, sh, a0.ctypes.data, a1.ctypes.data,
+                                              q.stream))
+    return astype(res, np.bool_) if is_bool else res
+
+
+def linspace(start, stop, /, num, *, dtype=None, device=None, endpoint=True, sycl_queue=None,
+             usm_type="device"):
+    """`num` evenly spaced values from start to stop, written on the device
+    (dpnp/tensor/_ctors.py:1340-1440): integer types are produced in the default floating type
+    and converted at the end."""
+    _check_usm_type(usm_type)
+    if endpoint not in (True, False):
+        raise TypeError("endpoint keyword argument must be of boolean type")
+    num = operator.index(num)
+    if num < 0:
+        raise ValueError("Number of points must be non-negative")
+    for v in (start, stop):
+        if not isinstance(v, (bool, int, float, np.integer, np.floating, np.bool_)):
+            raise ValueError("start and stop must be Python scalars.")
+    q = normalize_queue(sycl_queue, device)
+    if dtype is None:
+        dt = _default_fp
+    else:
+        dt = np.dtype(dtype)
+    int_dt = None
+    if dt.kind in "biu":
+        int_dt = dt if dtype is not None else None
+        dt = _default_fp
+    if dt.kind != "f":
+        raise ValueError(f"linspace does not produce arrays of type {dt}")
+    res = _empty((num,), dt, q, "C", usm_type)
+    if num:
+        a0, a1 = np.array([float(start)], dtype=dt), np.array([float(stop)], dtype=dt)
+        _lib.check(_lib.lib.dpb_linspace_affine(_lib.typenum_of(dt), res._ptr, num, a0.ctypes.data,
+                                                a1.ctypes.data, int(bool(endpoint)), q.stream))
+    return res if int_dt is None else astype(res, int_dt)

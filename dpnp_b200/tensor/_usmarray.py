@@ -351,6 +351,20 @@ class usm_ndarray:
             "stream": self._queue.stream or None,
         }
 
+    def __dlpack__(self, *, stream=None, max_version=None, dl_device=None, copy=None):
+        """DLPack capsule sharing this array's memory (dpnp/tensor/_usmarray.pyx:1130-1260).  Work
+        queued on the array's stream is finished first unless the consumer passes ``stream=-1``."""
+        from ._dlpack import to_dlpack_capsule
+
+        if stream != -1:
+            self._queue.wait()
+        return to_dlpack_capsule(self)
+
+    def __dlpack_device__(self):
+        from ._dlpack import dlpack_device
+
+        return dlpack_device(self)
+
     def __array_namespace__(self, api_version=None):
         from .. import tensor
 

@@ -563,6 +563,18 @@ int dpb_random_uniform(int typenum, void *dst, int64_t nelems, double lo, double
 int dpb_random_normal(int typenum, void *dst, int64_t nelems, double mean, double stddev,
                       uint64_t seed, uint64_t first_index, void *stream);
 
+/* Linear sequences written on the device into a contiguous array of `nelems` elements.
+ * `start`, `step`, `end` point to host values of the array's type.
+ * dpb_linspace_step: dst[i] = start + i*step, integers wrap (lin_space_step_impl,
+ * dpnp/tensor/libtensor/include/kernels/constructors.hpp:65-131; any real type).
+ * dpb_linspace_affine: dst[i] = start*(den-i)/den + end*i/den with den = nelems-1 when the
+ * end point is included, else nelems (lin_space_affine_impl, constructors.hpp:136-246;
+ * floating types). */
+int dpb_linspace_step(int typenum, void *dst, int64_t nelems, const void *start, const void *step,
+                      void *stream);
+int dpb_linspace_affine(int typenum, void *dst, int64_t nelems, const void *start, const void *end,
+                        int include_endpoint, void *stream);
+
 /* --------------------------------------------------------- introspection  */
 /* Name of the kernel family chosen by the most recent dispatch-level call in
  * this thread ("binary_contig_vec", "strided_rows", "transpose_tile", ...),
