@@ -601,7 +601,17 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
 
     ms = time_sharded(c3c if world > 1 else (lambda: dp.mean(x)), 10)
     rec("c3c_mean_f32_16384x65536", nb, ms)
-    del x
+    # running sums of the same matrix (every rank scans its own rows: no exchange is timed)
+    xs = dp.empty((rows, cols), dtype="f4")
+    ms = time_sharded(lambda: dp.cumsum(x, axis=1, out=xs), 5)
+    rec("cumsum_axis1_f32_16384x65536", 2 * nb, ms, note="read + write; one block per row, single pass")
+    ms = time_sharded(lambda: dp.cumsum(x, axis=0, out=xs), 5)
+    rec("cumsum_axis0_f32_16384x65536", 2 * nb, ms, note="read + write; one thread per column")
+    xflat, sflat = x.reshape(-1)[: 1 << 28], xs.reshape(-1)[: 1 << 28]
+    ms = time_sharded(lambda: dp.cumsum(xflat, out=sflat), 5)
+    rec("cumsum_flat_f32_2^28", 8 * (1 << 28) * world, ms,
+        note="one long row: segment totals, carry-ins, scan (input read twice; bytes counted once)")
+    del x, xs, xflat, sflat
 
     # C4: multiply(a.transpose(2,0,1), b), `a` sharded along its leading axis
     ja = 1024 // world

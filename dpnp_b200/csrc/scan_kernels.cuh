@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kScanThreads)
 }
 
 // `cols` columns are unit-stride in src and dst; a thread owns one column of one batch entry
-// and walks the L rows (stride r_src / r_dst), four loads in flight.
+// and walks the L rows (stride r_src / r_dst), eight loads in flight.
 template <class R>
 __global__ void __launch_bounds__(kScanThreads)
     scan_cols_kernel(const typename R::In *src, typename R::Out *dst, RedMeta batch, int64_t nbatch,
@@ -204,12 +204,13 @@ __global__ void __launch_bounds__(kScanThreads)
         typename R::Out *q = dst + o_dst + c + dst_shift * r_dst;
         Acc acc = R::identity();
         int64_t r = 0;
-        for (; r + 4 <= L; r += 4) {
-            In x[4];
+        constexpr int U = 8;   // loads in flight per thread
+        for (; r + U <= L; r += U) {
+            In x[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) x[u] = p[(r + u) * r_src];
+            for (int u = 0; u < U; ++u) x[u] = p[(r + u) * r_src];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 acc = R::combine(acc, R::load(x[u], r + u));
                 q[(r + u) * r_dst] = R::finish(acc);
             }
