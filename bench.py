@@ -19,9 +19,12 @@ synthetic (seeded uniform draws with the example's ranges).
            of the 26 ufunc launches / their summed CUDA-event durations.
 `cpu_baseline`: the C restatement of the chain (oracle/, OpenMP over all host
            cores) on a bounded sample; same 552 B/option accounting.
-`ops`    : the other benchmark configurations (add f32 2^24; fused Black-Scholes;
-           sum axis=1 / axis=0 / mean of f32 16384x65536; transposed broadcast
-           multiply; max/argmax of int32 (8, 2^29)), each timed on its own.
+`ops`    : the other benchmark configurations (add f32 2^24; the Black-Scholes
+           chain hand-fused and through the `fuse` front-end; sum axis=1 / axis=0 /
+           mean and running sums of f32 16384x65536; transposed broadcast multiply;
+           max/argmax of int32 (8, 2^29)) and one representative shape per kernel
+           family, each timed on its own.  Kernels of a few hundred microseconds
+           are timed over several back-to-back calls per sample.
 
 With N > 1 (torchrun, one rank per GPU) every rank prices its own 2^26 options
 (weak scaling, no data-path collective); the reduction configurations are

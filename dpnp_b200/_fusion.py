@@ -50,7 +50,7 @@ _COMPARISONS = {"less", "less_equal", "greater", "greater_equal", "equal", "not_
 _LOGICAL = {"logical_and", "logical_or"}
 _ALIASES = {"true_divide": "divide", "absolute": "abs", "power": "pow", "fabs": "abs"}
 
-_OPND_IMM, _OPND_ACC, _NO_DST = 64, 255, 255
+_OPND_IMM, _OPND_IN, _OPND_ACC, _NO_DST = 64, 128, 255, 255
 _MAX_INSTR, _MAX_IMM, _MAX_IN, _MAX_OUT, _MAX_REG = 192, 48, 12, 8, 24
 
 
@@ -280,7 +280,7 @@ def is_traced(*values):
 class _Program:
     """A compiled trace: instruction words plus the recipe for binding a call's arrays."""
 
-    def __init__(self, tr, in_slots, results_tree, result_nodes):
+    def __init__(self, tr, results_tree, result_nodes):
         self.dtype = tr.dtype
         self.results_tree = results_tree
         roots = list(dict.fromkeys(list(tr.stores.values()) + result_nodes))
@@ -307,14 +307,14 @@ class _Program:
             stack = [(i, False)]
             while stack:
                 j, done = stack.pop()
-                if j in seen or nodes[j][0] == "imm":
+                if j in seen or nodes[j][0] in ("imm", "in"):
                     continue
                 if done:
                     seen.add(j)
                     order.append(j)
                     continue
                 stack.append((j, True))
-                ch = [c for c in children(j) if c not in seen and nodes[c][0] != "imm"]
+                ch = [c for c in children(j) if c not in seen and nodes[c][0] not in ("imm", "in")]
                 ch.sort(key=lambda c: depth[c])            # shallow first, deep last
                 for c in reversed(ch):
                     stack.append((c, False))
@@ -349,13 +349,17 @@ class _Program:
             store_list.append((v, len(self.out_bind)))
             self.out_bind.append(("new",))
         # A store is issued right after its value is computed (the value is still in the
-        # accumulator) unless the destination is an argument that a later LOAD still reads;
+        # accumulator) unless the destination is an argument that a later instruction still reads;
         # such stores wait until the end and keep their value in a register.
-        in_pos = {nodes[j][1]: pos[j] for j in order if nodes[j][0] == "in"}
+        last_read = {}                         # argument slot -> last instruction that reads it
+        for p_, j in enumerate(order):
+            for c in children(j):
+                if nodes[c][0] == "in":
+                    last_read[nodes[c][1]] = p_
         eager, late = {}, []
         for v, out_i in store_list:
             bind = self.out_bind[out_i]
-            safe = bind[0] == "new" or in_pos.get(bind[1], -1) <= pos.get(v, end)
+            safe = bind[0] == "new" or last_read.get(bind[1], -1) <= pos.get(v, end)
             if v in pos and safe:
                 eager.setdefault(v, []).append(out_i)
             else:
@@ -365,9 +369,16 @@ class _Program:
                     n_uses[v] += 1
 
         imms, imm_index = [], {}
+        input_index = {}
+        self.in_slots = []
 
         def opnd(i, p, regs):
             k = nodes[i]
+            if k[0] == "in":                   # read straight from the argument, no register
+                if k[1] not in input_index:
+                    input_index[k[1]] = len(self.in_slots)
+                    self.in_slots.append(k[1])
+                return _OPND_IN + input_index[k[1]]
             if k[0] == "imm":
                 if k[1] not in imm_index:
                     imm_index[k[1]] = len(imms)
@@ -378,18 +389,11 @@ class _Program:
             return regs[i]
 
         code, regs, free, n_reg = [], {}, [], 0
-        input_index = {}
-        self.in_slots = []
         for p, j in enumerate(order):
             k = nodes[j]
             # the result needs a register unless its single use is the very next instruction
             only_next = (n_uses[j] == 1 and last_use[j] == p + 1) or (n_uses[j] == 0 and j in eager)
-            if k[0] == "in":
-                if k[1] not in input_index:
-                    input_index[k[1]] = len(self.in_slots)
-                    self.in_slots.append(k[1])
-                word = (_OPS["load"], input_index[k[1]], 0, 0)
-            elif k[0] == "un":
+            if k[0] == "un":
                 word = (_OPS[k[1]], opnd(k[2], p, regs), 0, 0)
             elif k[0] == "bin":
                 oa, ob = opnd(k[2], p, regs), opnd(k[3], p, regs)
@@ -420,25 +424,17 @@ class _Program:
             for out_i in eager.get(j, ()):             # stores do not disturb the accumulator
                 code.append(_OPS["store"] | _NO_DST << 8 | _OPND_ACC << 16 | out_i << 24)
         for v, out_i in late:
-            k = nodes[v]
-            if k[0] == "imm":
-                if k[1] not in imm_index:
-                    imm_index[k[1]] = len(imms)
-                    imms.append(struct.unpack("<d", k[1])[0])
-                a = _OPND_IMM + imm_index[k[1]]
-            else:
-                a = regs[v]
+            a = opnd(v, -1, regs) if nodes[v][0] in ("imm", "in") else regs[v]
             code.append(_OPS["store"] | _NO_DST << 8 | a << 16 | out_i << 24)
         if (len(code) > _MAX_INSTR or len(imms) > _MAX_IMM or len(self.in_slots) > _MAX_IN or
-                len(self.out_bind) > _MAX_OUT or n_reg > min(_MAX_REG, _OPND_IMM)):
+                len(self.out_bind) > _MAX_OUT or n_reg > min(_MAX_REG, _OPND_IMM) or
+                len(imms) > _OPND_IN - _OPND_IMM):
             raise FusionUnsupported("chain exceeds the limits of the interpreter")
         self.n_reg = n_reg
         self.n_instr = len(code)
         self.code = (C.c_uint64 * max(1, len(code)))(*code)
         self.imm = (C.c_double * max(1, len(imms)))(*imms)
         self.n_imm = len(imms)
-        self.result_nodes = result_nodes
-        self.node_kind = {v: nodes[v] for v in result_nodes}
 
     def listing(self):
         """Human-readable instruction list (for tests and debugging)."""
@@ -581,7 +577,7 @@ class _Fused:
         for slot in tr.stores:
             if scalar_slots[slot]:
                 raise FusionUnsupported("store into a size-1 array")
-        prog = _Program(tr, None, results_tree, list(dict.fromkeys(result_nodes)))
+        prog = _Program(tr, results_tree, list(dict.fromkeys(result_nodes)))
         prog.scalar_slots = scalar_slots
         return prog
 

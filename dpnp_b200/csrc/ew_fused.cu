@@ -31,6 +31,7 @@ constexpr int kFusedMaxReg = 24;
 
 // operand encoding (8 bits)
 constexpr unsigned kOpndImm = 64;      // 64 + i: immediate i
+constexpr unsigned kOpndIn = 128;      // 128 + i: input array i, read where it is used
 constexpr unsigned kOpndAcc = 255;     // result of the previous instruction
 constexpr unsigned kNoDst = 255;       // result stays in the accumulator only
 
@@ -132,11 +133,37 @@ __global__ void __launch_bounds__(kFusedThreads)
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = T(0);
 
+    // the thread's K elements of input array i (one element broadcast, 16-byte loads, or
+    // guarded element loads on the ragged tail / unaligned arrays)
+    auto load_input = [&](unsigned i, T(&v)[K]) {
+        const T *src = static_cast<const T *>(prm.in[i]);
+        if (prm.in_scalar[i]) {
+            const T c = src[0];
+#pragma unroll
+            for (int k = 0; k < K; ++k) v[k] = c;
+        }
+        else if (whole && prm.vector_io) {
+#pragma unroll
+            for (int k = 0; k < K; k += VW) {
+                V x = load_vec<V>(src + base + k);
+#pragma unroll
+                for (int j = 0; j < VW; ++j) v[k + j] = x.v[j];
+            }
+        }
+        else {
+#pragma unroll
+            for (int k = 0; k < K; ++k) v[k] = (base + k < n) ? src[base + k] : T(0);
+        }
+    };
+
     // operand -> v (the accumulator is copied; used where the value must outlive `acc`)
     auto fetch = [&](unsigned x, T(&v)[K]) {
         if (x == kOpndAcc) {
 #pragma unroll
             for (int k = 0; k < K; ++k) v[k] = acc[k];
+        }
+        else if (x >= kOpndIn) {
+            load_input(x - kOpndIn, v);
         }
         else if (x >= kOpndImm) {
             const T c = static_cast<T>(prm.imm[x - kOpndImm]);
@@ -162,24 +189,7 @@ __global__ void __launch_bounds__(kFusedThreads)
         const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
         const bool swap = (w >> 40) & 1;
         if (op == DPB_FUSED_LOAD) {
-            const T *src = static_cast<const T *>(prm.in[oa]);
-            if (prm.in_scalar[oa]) {
-                const T c = src[0];
-#pragma unroll
-                for (int k = 0; k < K; ++k) acc[k] = c;
-            }
-            else if (whole && prm.vector_io) {
-#pragma unroll
-                for (int k = 0; k < K; k += VW) {
-                    V x = load_vec<V>(src + base + k);
-#pragma unroll
-                    for (int j = 0; j < VW; ++j) acc[k + j] = x.v[j];
-                }
-            }
-            else {
-#pragma unroll
-                for (int k = 0; k < K; ++k) acc[k] = (base + k < n) ? src[base + k] : T(0);
-            }
+            load_input(oa, acc);
         }
         else if (op == DPB_FUSED_STORE) {
             T *dstp = static_cast<T *>(prm.out[ob]);
@@ -236,9 +246,10 @@ __global__ void __launch_bounds__(kFusedThreads)
 
 namespace {
 
-bool operand_ok(unsigned x, int n_reg, int n_imm, bool first)
+bool operand_ok(unsigned x, int n_reg, int n_imm, int n_in, bool first)
 {
     if (x == kOpndAcc) return !first;
+    if (x >= kOpndIn) return static_cast<int>(x - kOpndIn) < n_in;
     if (x >= kOpndImm) return static_cast<int>(x - kOpndImm) < n_imm;
     return static_cast<int>(x) < n_reg;
 }
@@ -288,13 +299,13 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
         bool ok = op >= 0 && op < DPB_FUSED_OP_COUNT;
         if (ok && op == DPB_FUSED_LOAD) ok = static_cast<int>(oa) < prog->n_in;
         else if (ok && op == DPB_FUSED_STORE)
-            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && static_cast<int>(ob) < prog->n_out;
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, prog->n_in, first) && static_cast<int>(ob) < prog->n_out;
         else if (ok && op == DPB_FUSED_SELECT)
-            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && operand_ok(ob, prog->n_reg, prog->n_imm, first) &&
-                 operand_ok(oc, prog->n_reg, prog->n_imm, first);
-        else if (ok && op < DPB_FUSED_FIRST_BINARY) ok = operand_ok(oa, prog->n_reg, prog->n_imm, first);
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, prog->n_in, first) && operand_ok(ob, prog->n_reg, prog->n_imm, prog->n_in, first) &&
+                 operand_ok(oc, prog->n_reg, prog->n_imm, prog->n_in, first);
+        else if (ok && op < DPB_FUSED_FIRST_BINARY) ok = operand_ok(oa, prog->n_reg, prog->n_imm, prog->n_in, first);
         else if (ok)
-            ok = operand_ok(oa, prog->n_reg, prog->n_imm, first) && operand_ok(ob, prog->n_reg, prog->n_imm, first);
+            ok = operand_ok(oa, prog->n_reg, prog->n_imm, prog->n_in, first) && operand_ok(ob, prog->n_reg, prog->n_imm, prog->n_in, first);
         if (ok && op != DPB_FUSED_STORE) ok = dst == kNoDst || static_cast<int>(dst) < prog->n_reg;
         if (!ok) return set_error(DPB_ERR_VALUE, "fused program: malformed instruction");
         prm.code[pc] = w;

@@ -22,12 +22,14 @@ struct ScanPlan {
 
 typedef int (*scan_fn_t)(const ScanPlan &plan, const void *src, void *dst, cudaStream_t stream);
 
+// Elements per thread and chunk: four 16-byte loads in flight, bounded by the registers the
+// accumulators take.
 template <class R> constexpr int scan_items()
 {
-    constexpr int by_in = 16 / static_cast<int>(sizeof(typename R::In));
-    constexpr int by_acc = 64 / static_cast<int>(sizeof(typename R::Acc));
+    constexpr int by_in = 64 / static_cast<int>(sizeof(typename R::In));
+    constexpr int by_acc = 128 / static_cast<int>(sizeof(typename R::Acc));
     constexpr int v = by_in < by_acc ? by_in : by_acc;
-    return v < 2 ? 2 : (v > 8 ? 8 : v);
+    return v < 2 ? 2 : (v > 16 ? 16 : v);
 }
 
 template <class R>
@@ -77,10 +79,14 @@ template <class R> int launch_scan(const ScanPlan &plan, const void *vsrc, void 
 
     const bool unit = plan.s_src == 1 && plan.s_dst == 1;
     // whole-thread vector accesses: rows start on the vector grid in both arrays
-    bool vec = unit && plan.dst_shift == 0 && is_aligned(src, sizeof(In) * ITEMS) &&
-               is_aligned(dst, std::min<size_t>(16, sizeof(Out) * ITEMS));
+    // (a thread's first element is a multiple of ITEMS, and ITEMS elements are whole 16-byte
+    // pieces of either type, so 16-byte aligned row starts are all that is needed)
+    constexpr int64_t in16 = sizeof(In) >= 16 ? 1 : 16 / sizeof(In);
+    constexpr int64_t out16 = sizeof(Out) >= 16 ? 1 : 16 / sizeof(Out);
+    bool vec = unit && plan.dst_shift == 0 && ITEMS % in16 == 0 && ITEMS % out16 == 0 &&
+               is_aligned(src, 16) && is_aligned(dst, 16);
     for (int i = 0; i < plan.iter_nd; ++i)
-        vec = vec && plan.iter_src[i] % ITEMS == 0 && plan.iter_dst[i] % ITEMS == 0;
+        vec = vec && plan.iter_src[i] % in16 == 0 && plan.iter_dst[i] % out16 == 0;
     const int64_t chunk = int64_t(kScanThreads) * ITEMS;
     int64_t nseg = 1, seg_len = L;
     if (nrows < target && L > 4 * chunk) {

@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kScanThreads)
 }
 
 // `cols` columns are unit-stride in src and dst; a thread owns one column of one batch entry
-// and walks the L rows (stride r_src / r_dst), eight loads in flight.
+// and walks the L rows (stride r_src / r_dst) with 8 to 32 loads in flight.
 template <class R>
 __global__ void __launch_bounds__(kScanThreads)
     scan_cols_kernel(const typename R::In *src, typename R::Out *dst, RedMeta batch, int64_t nbatch,
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(kScanThreads)
         typename R::Out *q = dst + o_dst + c + dst_shift * r_dst;
         Acc acc = R::identity();
         int64_t r = 0;
-        constexpr int U = 8;   // loads in flight per thread
+        // loads in flight per thread: 128 bytes' worth
+        constexpr int U = sizeof(In) >= 16 ? 8 : (128 / sizeof(In) > 32 ? 32 : (128 / sizeof(In) < 8 ? 8 : 128 / sizeof(In)));
         for (; r + U <= L; r += U) {
             In x[U];
 #pragma unroll

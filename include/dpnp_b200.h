@@ -486,7 +486,8 @@ int dpb_black_scholes_f64(int64_t n, const double *price, const double *strike, 
  * is broadcast.  Comparisons and logical operators give 1.0 / 0.0, SELECT tests != 0.
  *
  * Instruction word: op | dst << 8 | a << 16 | b << 24 | c << 32 | swap << 40.  Operands
- * a, b, c: 0..63 register, 64+i immediate i, 255 the result of the previous instruction.
+ * a, b, c: 0..63 register, 64+i immediate i, 128+i input array i (read where it is used, so
+ * inputs need no LOAD and no register), 255 the result of the previous instruction.
  * A binary instruction computes op(a, b), or op(b, a) when swap is set (so that the
  * previous result can always be given as a, where the interpreter works in place).
  * dst: a register, or 255 when only the next instruction reads the result.

@@ -38,6 +38,9 @@ def emulate(prog, inputs, n):
         if x == 255:
             assert not first
             return acc
+        if x >= 128:                      # an argument, read where it is used
+            r = np.array(inputs[x - 128], dtype=dt, copy=True)
+            return np.full(n, r.reshape(-1)[0], dt) if r.size == 1 else r.reshape(-1)
         if x >= 64:
             return np.full(n, imm[x - 64], dt)
         return regs[x]
@@ -112,11 +115,12 @@ def test_black_scholes_chain_program():
     P, S, T = rng.uniform(10, 50, n), rng.uniform(10, 50, n), rng.uniform(1, 2, n)
     call, put = np.zeros(n), np.zeros(n)
     prog, outs, _, ref = run_both(black_scholes, [P, S, T, call, put], (0.1, 0.2))
-    # a - b is shared, T * mr is shared, no intermediate is stored: 3 loads, 2 stores
+    # a - b is shared, T * mr is shared, no intermediate is stored; the arguments are read
+    # where they are used and take no register
     ops = [l[0] for l in prog.listing()]
-    assert ops.count("load") == 3 and ops.count("store") == 2
+    assert ops.count("load") == 0 and ops.count("store") == 2 and len(prog.in_slots) == 3
     assert ops.count("subtract") == 4 and ops.count("erf") == 2 and ops.count("exp") == 1
-    assert prog.n_reg <= 8
+    assert prog.n_reg <= 5
     assert [b for b in prog.out_bind] == [("slot", 3), ("slot", 4)]
     np.testing.assert_array_equal(outs[0], ref[3])
     np.testing.assert_array_equal(outs[1], ref[4])
@@ -150,9 +154,12 @@ def test_read_then_write_of_the_same_argument_and_inplace_operators():
     np.testing.assert_array_equal(outs[binds.index(("slot", 0))], ref_arrays[0])
     np.testing.assert_array_equal(outs[binds.index(("slot", 1))], ref_arrays[1])
     np.testing.assert_array_equal(outs[binds.index(("new",))], ref)
-    # stores into arguments that a later LOAD reads come after that LOAD
-    ops = [l[0] for l in prog.listing()]
-    assert max(i for i, o in enumerate(ops) if o == "load") < min(i for i, o in enumerate(ops) if o == "store")
+    # a store into an argument comes after the last instruction that reads that argument
+    lst = prog.listing()
+    for i, (op, dst, a, b, c) in enumerate(lst):
+        if op == "store" and prog.out_bind[b][0] == "slot":
+            code = 128 + prog.in_slots.index(prog.out_bind[b][1]) if prog.out_bind[b][1] in prog.in_slots else None
+            assert all(code not in l[2:] for l in lst[i + 1:] if l[0] != "store")
 
 
 def test_size_one_arrays_broadcast_and_out_keyword():

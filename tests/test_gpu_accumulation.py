@@ -110,3 +110,100 @@ def test_views_dtype_out_and_include_initial():
     assert _lib.last_kernel() == "scan_cols"
     dp.cumsum(dp.zeros((5000, 512), dtype="f4"), axis=1)
     assert _lib.last_kernel() == "scan_rows_vec"
+
+
+# ---- the known-answer cases of the reference's own tests
+# (dpnp/tests/tensor/test_tensor_accumulation.py); expected values are the closed forms the
+# tests assert, never the operation under test.
+REF = "dpnp/tests/tensor/test_tensor_accumulation.py"
+
+
+@pytest.mark.parametrize("dt", ["i1", "i2", "i4", "i8"])
+def test_reference_cumsum_of_plus_and_minus_ones(dt):
+    """:68-127 -- contiguous, strided, reversed, along axis 0 of a matrix and of a strided view;
+    the result type is the (possibly wrapping) input type."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    n = 10000
+    ar = np.arange(n).astype(dt)
+    expected = np.concatenate((1 + ar, ar[::-1]))
+    x = dev(np.repeat(np.array([1, -1], dtype=dt), n)).get_array()
+    np.testing.assert_array_equal(dp.asnumpy(dpt.cumulative_sum(x, dtype=dt)), expected)
+    x = dev(np.repeat(np.array([1, -1], dtype=dt), 2 * n)).get_array()[1::2]
+    np.testing.assert_array_equal(dp.asnumpy(dpt.cumulative_sum(x, dtype=dt)), expected)
+    x2 = dev(np.repeat(np.array([-1, 1], dtype=dt), 2 * n)).get_array()[-1::-2]
+    np.testing.assert_array_equal(dp.asnumpy(dpt.cumulative_sum(x2, dtype=dt)), expected)
+    n0, n1 = 1000, 173
+    ar = np.arange(n0).astype(dt)
+    expected = np.concatenate((1 + ar, ar[::-1]))[:, None]
+    m = np.tile(np.repeat(np.array([1, -1], dtype=dt), n0)[:, None], (1, n1))
+    r = dp.asnumpy(dpt.cumulative_sum(dev(m).get_array(), dtype=dt, axis=0))
+    assert np.all(r == expected)
+    m2 = np.tile(np.repeat(np.array([1, -1], dtype=dt), 2 * n0)[:, None], (1, n1))
+    r = dp.asnumpy(dpt.cumulative_sum(dev(m2).get_array()[1::2, ::-1], dtype=dt, axis=0))
+    assert np.all(r == expected)
+
+
+def test_reference_scalar_identity_and_basic_cases():
+    """:129-173 (scalar input, include_initial identities), :372-404 (cumprod, logcumsumexp),
+    :417-428 (closed form of a geometric series), :430-438 (gh-1901), :443-451 (gh-2017)."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    s = dev(np.asarray(1, dtype="i8")).get_array()
+    r = dpt.cumulative_sum(s)
+    assert r.ndim == 0 and int(dp.asnumpy(r)) == 1
+    np.testing.assert_array_equal(dp.asnumpy(dpt.cumulative_sum(s, include_initial=True)), [0, 1])
+    x = dp.ones((3, 5), dtype="i4").get_array()
+    assert np.all(dp.asnumpy(dpt.cumulative_sum(x, axis=0, include_initial=True))[0, :] == 0)
+    assert np.all(dp.asnumpy(dpt.cumulative_sum(x, axis=1, include_initial=True))[:, 0] == 0)
+    r = dpt.cumulative_sum(dp.ones(5, dtype="i4").get_array(), include_initial=True)
+    assert r.shape == (6,) and dp.asnumpy(r)[0] == 0
+    assert dp.asnumpy(dpt.cumulative_prod(dp.zeros(5, dtype="i4").get_array(), include_initial=True))[0] == 1
+    assert dp.asnumpy(dpt.cumulative_logsumexp(dp.ones(5, dtype="f4").get_array(), include_initial=True))[0] == -np.inf
+
+    r = dpt.cumulative_prod(dp.full(50, 2, dtype="i8").get_array())
+    np.testing.assert_array_equal(dp.asnumpy(r), 2 ** np.arange(1, 51, dtype="i8"))
+    r = dpt.cumulative_prod(dev(np.tile(np.array([2, 0.5], dtype="f4"), 10000)).get_array())
+    np.testing.assert_array_equal(dp.asnumpy(r), np.tile(np.array([2, 1], dtype="f4"), 10000))
+    r = dpt.cumulative_logsumexp(dp.ones(1000, dtype="f4").get_array())
+    tol = 4 * np.finfo("f4").resolution
+    np.testing.assert_allclose(dp.asnumpy(r), 1 + np.log(np.arange(1, 1001, dtype="f4")), atol=tol, rtol=tol)
+    for fpdt in ("f2", "f4", "f8"):
+        n = 128
+        k = np.arange(n, dtype="f8")
+        closed = -n + k + np.log1p(-np.exp(-k - 1)) - np.log1p(-np.exp(-1.0))
+        r = dpt.cumulative_logsumexp(dev(np.arange(-n, 0).astype(fpdt)).get_array())
+        tol = 4 * np.finfo(fpdt).eps
+        np.testing.assert_allclose(dp.asnumpy(r).astype("f8"), closed, atol=tol * 40, rtol=tol)
+    for p in (257, 260, 273, 280, 509, 512):
+        n = p * p
+        r = dpt.cumulative_sum(dp.ones(n, dtype="i4").get_array(), dtype="i4")
+        np.testing.assert_array_equal(dp.asnumpy(r), np.arange(1, n + 1, dtype="i4"))
+    for dt in ("i1", "i2", "i4", "i8", "f2", "f4", "f8"):
+        r = dpt.cumulative_sum(dev(np.array([-1, 1], dtype=dt)).get_array(), dtype="?")
+        assert r.dtype == np.dtype("?") and np.all(dp.asnumpy(r))
+
+
+def test_reference_nan_propagation_and_type_matrix():
+    """:314-349 (NaN stays from its position on), :198-237 (default and requested result types)."""
+    import dpnp_b200 as dp
+    from dpnp_b200.tensor._type_utils import _default_accumulation_dtype
+
+    dpt = dp.tensor
+    for fn in (dpt.cumulative_sum, dpt.cumulative_prod, dpt.cumulative_logsumexp):
+        x = np.ones(10, dtype="f4")
+        x[4] = np.nan
+        r = dp.asnumpy(fn(dev(x).get_array()))
+        assert np.all(np.isnan(r[4:])) and not np.any(np.isnan(r[:4]))
+    for arg in ("?", "i1", "u1", "i2", "u2", "i4", "u4", "i8", "u8", "f2", "f4", "f8"):
+        m = dp.ones(100, dtype=arg).get_array()
+        r = dpt.cumulative_sum(m)
+        assert r.dtype == _default_accumulation_dtype(np.dtype(arg))
+        if arg != "?":
+            np.testing.assert_array_equal(dp.asnumpy(r), np.arange(1, 101).astype(r.dtype))
+        for out in ("i4", "u8", "f4", "f8"):
+            r = dpt.cumulative_sum(m, dtype=out)
+            assert r.dtype == np.dtype(out)
+            np.testing.assert_array_equal(dp.asnumpy(r), np.arange(1, 101).astype(out))
