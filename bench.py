@@ -460,9 +460,9 @@ def run_gpu_arm(args):
 
 
 # dram bytes read+written per launch of ew_contig_vec on 2^26 f64 operands: the ncu capture summarised in
-# profiles/ew_contig_vec_f64_multiply_2p25.md measured 0.95 x the algorithmic bytes on 2^25 elements; scaled
-# by the element count and averaged over the step's 10 array-array and 16 unary/array-scalar launches.
-TRAFFIC_EW_CONTIG_F64 = 1.22e9
+# profiles/ew_contig_vec_f64_multiply_2p25.md measured 0.94 x the algorithmic bytes on 2^25 elements; scaled
+# by the element count and averaged over the step's 13 array-array and 13 unary/array-scalar launches.
+TRAFFIC_EW_CONTIG_F64 = 1.265e9
 
 
 def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, strike, tt, call, put):

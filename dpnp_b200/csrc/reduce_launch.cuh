@@ -177,11 +177,14 @@ int launch_outer(const typename R::In *arg, void *res, const RedMeta &batch, con
         const int64_t ncg = ceil_div(C, int64_t(kRedThreads) * (vec ? VEC : 1));
         const int64_t nblocks = nbatch * nslab * ncg;
         const int grid = static_cast<int>(std::min<int64_t>(nblocks, int64_t(1) << 30));
+        // loads in flight per thread: fewer for wide accumulators (value + index), which
+        // otherwise cost the registers that occupancy needs
+        constexpr int UC = sizeof(typename R::Acc) > 8 ? UNROLL : 2 * UNROLL;
         if (vec)
-            reduce_outer_kernel<R, VEC, 2 * UNROLL, 1><<<grid, kRedThreads, 0, stream>>>(
+            reduce_outer_kernel<R, VEC, UC, 1><<<grid, kRedThreads, 0, stream>>>(
                 arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
         else
-            reduce_outer_kernel<R, 1, 2 * UNROLL, 1><<<grid, kRedThreads, 0, stream>>>(
+            reduce_outer_kernel<R, 1, UC, 1><<<grid, kRedThreads, 0, stream>>>(
                 arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
         note_kernel(vec ? "reduce_outer_cols_vec" : "reduce_outer_cols_scalar");
     }
