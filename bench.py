@@ -595,7 +595,15 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
         return sharded.allreduce_sum_ordered(part) if dist is not None else part
 
     ms = time_sharded(c3b, 10)
-    rec("c3b_sum_axis0_f32_16384x65536", nb, ms, note="partials combined in rank order" if world > 1 else None)
+    rec("c3b_sum_axis0_f32_16384x65536", nb, ms,
+        note="partials gathered over NCCL and summed in a fixed order on every rank" if world > 1 else None)
+    if dist is not None:
+        # the combined result against a plain NCCL all-reduce of the same partials
+        import torch
+        chk = torch.from_numpy(dp.sum(x, axis=0).asnumpy()).cuda()
+        dist.all_reduce(chk)
+        if not np.allclose(c3b().asnumpy(), chk.cpu().numpy(), rtol=1e-4, atol=1e-2):
+            raise RuntimeError("sharded sum over axis 0 disagrees with an all-reduce of the partials")
 
     def c3c():
         part = dp.sum(x)

@@ -37,70 +37,61 @@ def _dist():
     return dist
 
 
-def _to_torch(x):
-    """(torch tensor sharing memory with x, is_device)."""
+def _gather(x, group=None):
+    """List of every rank's `x` as NumPy arrays (host input)."""
     import torch
 
-    if isinstance(x, np.ndarray):
-        return torch.from_numpy(np.ascontiguousarray(x)), False
-    arr = x.get_array() if hasattr(x, "get_array") else x
+    dist = _dist()
+    t = torch.from_numpy(np.ascontiguousarray(x))
+    t = t.reshape(-1) if t.dim() == 0 else t
+    outs = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(outs, t, group=group)
+    return outs
+
+
+def _on_queue_stream(arr):
+    """Context in which torch enqueues on the array's own stream: the collective is then ordered
+    with the library's kernels by the stream, and the host does not wait for either."""
+    import torch
+
+    q = arr.sycl_queue
+    return torch.cuda.stream(torch.cuda.ExternalStream(q.stream, device=f"cuda:{q.device}"))
+
+
+def _as_torch(arr):
+    """torch tensor over the memory of a C-contiguous device array of the library."""
+    import torch
+
     if not arr.flags.c_contiguous:
         raise ValueError("collectives need C-contiguous device arrays")
-    arr.sycl_queue.wait()  # the collective runs on torch's stream
     dt = arr.dtype
     if dt.kind == "u" and dt.itemsize > 1:
         # torch has no wide unsigned collectives: move the bits as signed integers of the same size
         import dpnp_b200.tensor as dpt
         arr = dpt.usm_ndarray._view(arr.usm_data, arr._ptr, arr.shape, arr.strides, np.dtype(f"i{dt.itemsize}"),
                                     arr.sycl_queue)
-    return torch.as_tensor(arr, device=f"cuda:{arr.sycl_queue.device}"), True
-
-
-def _gather(x, group=None):
-    """List of every rank's `x` (as NumPy arrays for host input, torch device tensors otherwise)."""
-    import torch
-
-    dist = _dist()
-    t, on_device = _to_torch(x)
-    t = t.reshape(-1) if t.dim() == 0 else t
-    outs = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(outs, t, group=group)
-    if on_device:
-        torch.cuda.synchronize()
-    return outs, on_device
+    return torch.as_tensor(arr, device=f"cuda:{arr.sycl_queue.device}")
 
 
 def allreduce_sum_ordered(partial, group=None):
-    """Sum of the ranks' partials, added in rank order on every rank."""
-    outs, on_device = _gather(partial, group)
-    if not on_device:
+    """Sum of the ranks' partials, computed on every rank from the same gathered rows in the
+    same fixed order: all ranks get the same bits, whatever order the collective works in."""
+    if isinstance(partial, np.ndarray) or np.isscalar(partial):
+        outs = _gather(partial, group)
         acc = outs[0].numpy().copy()
         for o in outs[1:]:
             acc = acc + o.numpy()
         return acc.reshape(np.shape(partial))
     import dpnp_b200 as dp
 
-    acc = None
-    for o in outs:
-        part = dp.asarray(_torch_to_dpnp(o, partial))
-        acc = part if acc is None else acc + part
-    return acc.reshape(partial.shape)
-
-
-def _torch_to_dpnp(t, like):
-    """Copy a torch device tensor into a new array of the library (device-to-device)."""
-    import ctypes as C
-
-    import dpnp_b200 as dp
-    from dpnp_b200._lib import check, lib
-
-    out = dp.empty(tuple(t.shape), dtype=like.dtype)
-    q = out.sycl_queue
-    q.activate()
-    check(lib.dpb_memcpy(C.c_void_p(out.get_array()._ptr), C.c_void_p(t.data_ptr()), out.nbytes, 2,
-                         C.c_void_p(q.stream)))
-    q.wait()
-    return out
+    dist = _dist()
+    world = dist.get_world_size(group)
+    arr = partial.get_array() if hasattr(partial, "get_array") else partial
+    gathered = dp.empty((world, max(arr.size, 1)), dtype=arr.dtype, sycl_queue=arr.sycl_queue)
+    with _on_queue_stream(arr):
+        dist.all_gather_into_tensor(_as_torch(gathered.get_array()).view(-1), _as_torch(arr).reshape(-1),
+                                    group=group)
+    return dp.sum(gathered, axis=0, dtype=arr.dtype).reshape(partial.shape)
 
 
 def allreduce_extreme(partial, op="max", group=None):
@@ -108,13 +99,15 @@ def allreduce_extreme(partial, op="max", group=None):
     import torch
 
     dist = _dist()
-    t, on_device = _to_torch(partial)
     red = dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.MIN
-    dist.all_reduce(t, op=red, group=group)
-    if on_device:
-        torch.cuda.synchronize()
-        return partial
-    return t.numpy().reshape(np.shape(partial))
+    if isinstance(partial, np.ndarray) or np.isscalar(partial):
+        t = torch.from_numpy(np.ascontiguousarray(partial))
+        dist.all_reduce(t, op=red, group=group)
+        return t.numpy().reshape(np.shape(partial))
+    arr = partial.get_array() if hasattr(partial, "get_array") else partial
+    with _on_queue_stream(arr):
+        dist.all_reduce(_as_torch(arr), op=red, group=group)
+    return partial
 
 
 def combine_arg_extreme(value, global_index, op="max", group=None):
