@@ -376,7 +376,7 @@ def run_gpu_arm(args):
     # stays on one queue, as the API requires.
     from dpnp_b200.memory import StreamQueue
 
-    nchunks = 8
+    nchunks = args.e2e_chunks
     csz = n // nchunks
     queues = [StreamQueue(local_rank) for _ in range(3)]
     chunk_bufs = []
@@ -732,6 +732,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-configuration extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-chunks", type=int, default=16,
+                    help="pieces the batch is cut into for the pipelined end-to-end measurement")
     ap.add_argument("--profile-case", default=None, help="run one small case for an ncu capture: "
                     + ", ".join(PROFILE_CASES))
     args = ap.parse_args()
