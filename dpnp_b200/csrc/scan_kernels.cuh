@@ -82,27 +82,38 @@ __global__ void __launch_bounds__(kScanThreads)
         const In *p = src + o_src;
         Out *q = dst + o_dst + dst_shift * s_dst;
         Acc carry = carry_in ? carry_in[item] : R::identity();
-        for (int64_t base = begin; base < end; base += int64_t(kScanThreads) * ITEMS) {
+        // the thread's ITEMS raw elements of the chunk that starts at `base` (elements past the
+        // end are left unset and masked when they are used)
+        auto fetch = [&](int64_t base, In(&raw)[ITEMS]) {
             const int64_t i0 = base + int64_t(tid) * ITEMS;
-            Acc v[ITEMS];
-            const bool whole = i0 + ITEMS <= end;
-            if (VEC && whole) {
+            if (VEC && i0 + ITEMS <= end) {
                 constexpr int IV = (16 / sizeof(In)) < ITEMS ? (16 / sizeof(In)) : ITEMS;  // per access
 #pragma unroll
                 for (int g = 0; g < ITEMS; g += IV) {
                     const vec_t<In, IV> x = load_vec<vec_t<In, IV>>(p + i0 + g);
 #pragma unroll
-                    for (int j = 0; j < IV; ++j) v[g + j] = R::load(x.v[j], i0 + g + j);
+                    for (int j = 0; j < IV; ++j) raw[g + j] = x.v[j];
                 }
             }
             else {
 #pragma unroll
                 for (int i = 0; i < ITEMS; ++i) {
                     const int64_t e = i0 + i;
-                    if (e < end) v[i] = R::load(UNIT ? p[e] : p[e * s_src], e);
-                    else v[i] = R::identity();
+                    if (e < end) raw[i] = UNIT ? p[e] : p[e * s_src];
                 }
             }
+        };
+        constexpr int64_t kChunk = int64_t(kScanThreads) * ITEMS;
+        In raw[ITEMS];
+        if (begin < end) fetch(begin, raw);
+        for (int64_t base = begin; base < end; base += kChunk) {
+            const int64_t i0 = base + int64_t(tid) * ITEMS;
+            const bool whole = i0 + ITEMS <= end;
+            Acc v[ITEMS];
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) v[i] = (i0 + i < end) ? R::load(raw[i], i0 + i) : R::identity();
+            // the next chunk's loads are in flight while this one is scanned and stored
+            if (base + kChunk < end) fetch(base + kChunk, raw);
 #pragma unroll
             for (int i = 1; i < ITEMS; ++i) v[i] = R::combine(v[i - 1], v[i]);
             // inclusive scan of the thread totals inside the warp
