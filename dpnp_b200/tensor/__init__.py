@@ -14,6 +14,11 @@ from ._elementwise_funcs import (abs, add, ceil, cos, divide, equal, erf, exp, e
                                  logical_and, logical_not, logical_or, maximum, minimum, multiply,
                                  negative, not_equal, positive, pow, reciprocal, sign, sin, sqrt,
                                  square, subtract, tanh)
+from ._elementwise_funcs import (acos, acosh, angle, asin, asinh, atan, atan2, atanh, bitwise_and,
+                                 bitwise_invert, bitwise_left_shift, bitwise_or, bitwise_right_shift,
+                                 bitwise_xor, cbrt, conj, copysign, cosh, exp2, floor_divide, hypot, imag,
+                                 log2, log10, logaddexp, logical_xor, nextafter, proj, real, remainder,
+                                 round, rsqrt, signbit, sinh, tan, trunc)
 from ._manipulation_functions import (broadcast_arrays, broadcast_shapes, broadcast_to, expand_dims,
                                       flip, permute_dims, reshape, squeeze)
 from ._reduction import (all, any, argmax, argmin, count_nonzero, logsumexp, max, min, prod, reduce_hypot,

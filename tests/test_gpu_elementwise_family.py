@@ -209,3 +209,96 @@ def test_type_rules_and_strided_operands():
     f = np.linspace(-4, 4, 60).reshape(6, 10)
     got = dp.arctan2(dev(f)[:, ::-1], dev(f).T[:10, :6].T).asnumpy()
     assert ulps(got, np.arctan2(f[:, ::-1], f)) <= 4
+
+
+# ---- known-answer cases of the reference's own tests (dpnp/tests/tensor/elementwise/); the
+# expected values are the literals / NumPy results those tests assert.
+def test_reference_floor_divide_cases():
+    """test_floor_divide.py:80-147 (gh-1247, zero divisors, special values)."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    x = dp.ones(1, dtype="i4").get_array()
+    np.testing.assert_array_equal(dp.asnumpy(dpt.floor_divide(x, -2)), np.full(1, -1, "i4"))
+    x = dp.full(1, -1, dtype="i4").get_array()
+    np.testing.assert_array_equal(dp.asnumpy(dpt.floor_divide(x, 2)), np.full(1, -1, "i4"))
+    for dt in INTS:
+        xa = dev(np.arange(10, dtype=dt)).get_array()
+        r = dpt.floor_divide(xa, dev(np.zeros(10, dtype=dt)).get_array())
+        np.testing.assert_array_equal(dp.asnumpy(r), np.zeros(10, dtype=dt))
+
+    def fd(a, b):
+        return dp.asnumpy(dpt.floor_divide(dev(np.array([a], "f4")).get_array(), dev(np.array([b], "f4")).get_array()))
+
+    assert np.isnan(fd(np.inf, np.inf)[0])
+    r = fd(0.0, -1.0)
+    assert r[0] == 0 and np.signbit(r[0])                     # -0.0
+    assert fd(-1.0, 0.0)[0] == -np.inf
+    r = fd(-1.0, np.inf)
+    assert r[0] == 0 and np.signbit(r[0])                     # the literal the test asserts: -0.0
+    assert fd(np.inf, -1.0)[0] == -np.inf
+    assert np.isnan(fd(1.0, np.nan)[0])
+
+
+def test_reference_remainder_cases():
+    """test_remainder.py:80-153 (negative integers, zero divisors, negative floats, special values)."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    for dt in ("i1", "i2", "i4", "i8"):
+        x_np = np.arange(-5, -1, 1, dtype=dt)
+        x = dev(x_np).get_array()
+        assert (dp.asnumpy(dpt.remainder(x, 3)) == np.remainder(x_np, 3)).all()
+        assert (dp.asnumpy(dpt.remainder(3, x)) == np.remainder(3, x_np)).all()
+    for dt in ("i4", "u4"):
+        r = dpt.remainder(dp.ones(1, dtype=dt).get_array(), dp.zeros(1, dtype=dt).get_array())
+        assert (dp.asnumpy(r) == np.zeros(1, dtype=dt)).all()
+    for dt in ("f2", "f4", "f8"):
+        x_np = np.linspace(-5, 5, 20, dtype=dt)
+        x = dev(x_np).get_array()
+        tol = 8 * np.finfo(dt).resolution
+        np.testing.assert_allclose(dp.asnumpy(dpt.remainder(x, 3)), np.remainder(x_np, dt and np.dtype(dt).type(3)),
+                                   rtol=tol, atol=tol)
+        with np.errstate(all="ignore"):
+            np.testing.assert_allclose(dp.asnumpy(dpt.remainder(3, x)), np.remainder(np.dtype(dt).type(3), x_np),
+                                       rtol=tol, atol=tol)
+    lhs = [np.nan, np.inf, 0.0, -0.0, -0.0, 1.0, np.inf, -np.inf]
+    rhs = [np.nan, np.inf, -0.0, 1.0, 1.0, 0.0, 1.0, -1.0]
+    x_np, y_np = np.asarray(lhs, "f4"), np.asarray(rhs, "f4")
+    with np.errstate(all="ignore"):
+        np.testing.assert_allclose(dp.asnumpy(dpt.remainder(dev(x_np).get_array(), dev(y_np).get_array())),
+                                   np.remainder(x_np, y_np))
+
+
+def test_reference_shift_round_nextafter_cases():
+    """test_bitwise_left_shift.py:107-117 and test_bitwise_right_shift.py (a count of 64 gives 0),
+    test_round.py:109-123 (halves to even, signs of zero), test_nextafter.py:80-140."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    for dt in INTS:
+        x = dp.ones(255, dtype=dt).get_array()
+        y = dev(np.asarray(64, dtype=dt)).get_array()
+        assert not dp.asnumpy(dpt.bitwise_left_shift(x, y)).any()
+        assert not dp.asnumpy(dpt.bitwise_right_shift(x, y)).any()
+    for dt in FLOATS:
+        x = np.array([np.nan, np.inf, -np.inf, 1.5, 2.5, -1.5, -2.5, 0.0, -0.0], dtype=dt)
+        y = dp.asnumpy(dpt.round(dev(x).get_array()))
+        ref = np.round(x)
+        np.testing.assert_array_equal(y[1:], ref[1:])
+        assert np.isnan(y[0])
+        np.testing.assert_array_equal(np.signbit(y[1:]), np.signbit(ref[1:]))
+        x1 = dev(np.array([2.0, np.nan, np.nan], dtype=dt)).get_array()
+        x2 = dev(np.array([np.nan, 2.0, np.nan], dtype=dt)).get_array()
+        assert np.isnan(dp.asnumpy(dpt.nextafter(x1, x2))).all()
+        z1 = np.array([-0.0, 0.0, -0.0, 0.0], dtype=dt)
+        z2 = np.array([0.0, -0.0, -0.0, 0.0], dtype=dt)
+        yz = dp.asnumpy(dpt.nextafter(dev(z1).get_array(), dev(z2).get_array()))
+        assert (yz == 0).all()
+        np.testing.assert_array_equal(np.signbit(yz), np.signbit(z2))          # equal operands give x2
+        ones, twos = dp.ones(10, dtype=dt).get_array(), dp.full(10, 2, dtype=dt).get_array()
+        r = dp.asnumpy(dpt.nextafter(ones, twos))
+        assert (r > 0).all() and (r - np.ones(10, dt) == np.finfo(dt).eps).all()
+        zeros = dp.zeros(10, dtype=dt).get_array()
+        assert (dp.asnumpy(dpt.nextafter(zeros, ones)) > 0).all()
+        assert ((dp.asnumpy(dpt.nextafter(ones, zeros)) - np.ones(10, dt)) < 0).all()
