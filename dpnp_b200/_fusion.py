@@ -52,6 +52,7 @@ _ALIASES = {"true_divide": "divide", "absolute": "abs", "power": "pow", "fabs": 
 
 _OPND_IMM, _OPND_IN, _OPND_ACC, _NO_DST = 64, 128, 255, 255
 _MAX_INSTR, _MAX_IMM, _MAX_IN, _MAX_OUT, _MAX_REG = 192, 48, 12, 8, 24
+_MAX_CACHED = 256                  # compiled programs kept per fused function (oldest dropped first)
 
 
 class FusionUnsupported(Exception):
@@ -595,6 +596,8 @@ class _Fused:
                 prog = str(e) or "unsupported"
             except (AttributeError, TypeError, ValueError, NotImplementedError, IndexError) as e:
                 prog = f"{type(e).__name__}: {e}"
+            if len(self._cache) >= _MAX_CACHED:        # scalars are part of the key: keep it bounded
+                self._cache.pop(next(iter(self._cache)))
             self._cache[sig] = prog
         if isinstance(prog, str):
             return None, prog, arrays

@@ -56,6 +56,20 @@ def _deleter(ptr):
     _exported.pop(C.addressof(ptr.contents), None)
 
 
+_CAPSULE_DESTRUCTOR = C.CFUNCTYPE(None, C.c_void_p)
+
+
+@_CAPSULE_DESTRUCTOR
+def _capsule_destructor(capsule_addr):
+    """A capsule that was never consumed still owns its tensor: release it."""
+    try:
+        capsule = C.cast(capsule_addr, C.py_object)
+        if _api.PyCapsule_IsValid(capsule, _NAME):
+            _exported.pop(_api.PyCapsule_GetPointer(capsule, _NAME), None)
+    except Exception:                                    # interpreter shutdown: nothing to release
+        pass
+
+
 def to_dlpack_capsule(x):
     """Capsule named "dltensor" that shares the memory of `x`; the array stays alive until the
     consumer calls the deleter."""
@@ -76,7 +90,7 @@ def to_dlpack_capsule(x):
     m.manager_ctx = None
     m.deleter = _deleter
     _exported[C.addressof(m)] = (m, shape, strides, x)
-    return _api.PyCapsule_New(C.addressof(m), _NAME, None)
+    return _api.PyCapsule_New(C.addressof(m), _NAME, C.cast(_capsule_destructor, C.c_void_p))
 
 
 def dlpack_device(x):
