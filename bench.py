@@ -662,7 +662,7 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     return out
 
 
-PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "rows_bcast",
+PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "fuse_cheap", "rows_bcast",
                  "argmax_axis0", "sum_axis1",
                  "sum_axis0", "mean_all", "transpose_c4", "max_i32", "argmax_i32")
 
@@ -696,6 +696,19 @@ def profile_case(name, launches=3):
         c, u = dp.empty(n), dp.empty(n)
         chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
         fn = lambda: chain(p, s, t, c, u)
+    elif name == "fuse_cheap":
+        # 60 dependent multiply/add instructions with immediate operands: almost no arithmetic, so
+        # the capture shows what interpreting one instruction costs
+        n = 1 << 24
+        x, o = dp.random.uniform(1, 2, n), dp.empty(n)
+
+        def cheap(x_, o_):
+            v = x_
+            for _ in range(30):
+                v = v * 1.0001 + 0.5
+            o_[:] = v
+        chain = dp.fuse(cheap)
+        fn = lambda: chain(x, o)
     elif name == "rows_bcast":
         x, r, o = dp.random.uniform(-1, 1, (8192, 4096)), dp.random.uniform(-1, 1, 4096), dp.empty((8192, 4096))
         fn = lambda: dp.subtract(x, r, out=o)

@@ -35,10 +35,36 @@ constexpr unsigned kOpndIn = 128;      // 128 + i: input array i, read where it 
 constexpr unsigned kOpndAcc = 255;     // result of the previous instruction
 constexpr unsigned kNoDst = 255;       // result stays in the accumulator only
 
+// The host turns every instruction word into one or two micro-operations whose fields the
+// kernel can use as they are (operand kind resolved, shared-memory offsets multiplied out,
+// the first operand always the accumulator), so the device decodes with one 16-byte load.
+enum FusedKind : int32_t {
+    FK_MOVE_REG = 0,   // acc <- register
+    FK_MOVE_IMM,       // acc <- immediate
+    FK_MOVE_IN,        // acc <- input array
+    FK_STORE,          // output array <- acc (acc unchanged)
+    FK_STORE_ANY,      // output array <- any operand, acc untouched (aux2 = original operand code)
+    FK_SELECT,         // acc <- a ? b : c, operands by their original codes in b_off
+    FK_UNARY,          // acc <- op(acc)
+    FK_BIN_REG,        // acc <- op(acc, register)   (operands exchanged when swap is set)
+    FK_BIN_IN,         // acc <- op(acc, input array)
+    FK_BIN_ACC,        // acc <- op(acc, acc)
+    FK_BIN_IMM         // acc <- op(acc, immediate)
+};
+
+struct FusedUop {
+    int32_t kind_op;    // kind | op << 8 | swap << 16
+    int32_t dst_off;    // register to receive acc: offset in 16-byte groups, or -1
+    int32_t b_off;      // register operand: offset in 16-byte groups; SELECT: a | b << 8 | c << 16
+    int32_t aux;        // immediate / input / output index
+};
+
+constexpr int kFusedMaxUops = 2 * kFusedMaxInstr;
+
 struct FusedParams {
-    int32_t n_instr;
+    int32_t n_uop;
     int32_t vector_io;                  // every array pointer is 16-byte aligned
-    uint64_t code[kFusedMaxInstr];      // op | dst << 8 | a << 16 | b << 24 | c << 32 | swap << 40
+    FusedUop uop[kFusedMaxUops];
     double imm[kFusedMaxImm];
     const void *in[kFusedMaxIn];
     int32_t in_scalar[kFusedMaxIn];     // input is one element, broadcast
@@ -109,6 +135,39 @@ template <class T, int K, bool SWAP> DPB_D void fused_binary(int op, T (&acc)[K]
         break;
     }
 }
+
+// Second operand is one immediate for all K elements: no broadcast into registers.
+#define DPB_FUSED_BINS(CODE, EXPR)                                 \
+    case CODE:                                                     \
+        _Pragma("unroll") for (int k = 0; k < K; ++k) {            \
+            const T x = SWAP ? c : acc[k];                         \
+            const T y = SWAP ? acc[k] : c;                         \
+            acc[k] = (EXPR);                                       \
+        }                                                          \
+        break;
+template <class T, int K, bool SWAP> DPB_D void fused_binary_scalar(int op, T (&acc)[K], const T c)
+{
+    switch (op) {
+        DPB_FUSED_BINS(DPB_FUSED_ADD, (AddOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_SUBTRACT, (SubtractOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_MULTIPLY, (MultiplyOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_DIVIDE, (TrueDivideOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_MAXIMUM, (MaximumOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_MINIMUM, (MinimumOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_POW, (PowOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_LESS, as_flag<T>(LessOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_LESS_EQUAL, as_flag<T>(LessEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_GREATER, as_flag<T>(GreaterOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_GREATER_EQUAL, as_flag<T>(GreaterEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_EQUAL, as_flag<T>(EqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_NOT_EQUAL, as_flag<T>(NotEqualOp<T, T>::apply(x, y)))
+        DPB_FUSED_BINS(DPB_FUSED_LOGICAL_AND, ((x != T(0) && y != T(0)) ? T(1) : T(0)))
+        DPB_FUSED_BINS(DPB_FUSED_LOGICAL_OR, ((x != T(0) || y != T(0)) ? T(1) : T(0)))
+    default:
+        break;
+    }
+}
+#undef DPB_FUSED_BINS
 #undef DPB_FUSED_UN
 #undef DPB_FUSED_BIN
 
@@ -156,8 +215,33 @@ __global__ void __launch_bounds__(kFusedThreads)
         }
     };
 
-    // operand -> v (the accumulator is copied; used where the value must outlive `acc`)
-    auto fetch = [&](unsigned x, T(&v)[K]) {
+    auto load_reg = [&](int off, T(&v)[K]) {
+#pragma unroll
+        for (int g = 0; g < NV; ++g) {
+            const V t = regs[(off + g) * kFusedThreads + tid];
+#pragma unroll
+            for (int j = 0; j < VW; ++j) v[g * VW + j] = t.v[j];
+        }
+    };
+    auto store_out = [&](int i, const T(&v)[K]) {
+        T *dstp = static_cast<T *>(prm.out[i]);
+        if (whole && prm.vector_io) {
+#pragma unroll
+            for (int k = 0; k < K; k += VW) {
+                V x;
+#pragma unroll
+                for (int j = 0; j < VW; ++j) x.v[j] = v[k + j];
+                store_vec(dstp + base + k, x);
+            }
+        }
+        else {
+#pragma unroll
+            for (int k = 0; k < K; ++k)
+                if (base + k < n) dstp[base + k] = v[k];
+        }
+    };
+    // operand by its original 8-bit code (the rare paths: SELECT, stores of a non-accumulator)
+    auto fetch_any = [&](unsigned x, T(&v)[K]) {
         if (x == kOpndAcc) {
 #pragma unroll
             for (int k = 0; k < K; ++k) v[k] = acc[k];
@@ -171,74 +255,67 @@ __global__ void __launch_bounds__(kFusedThreads)
             for (int k = 0; k < K; ++k) v[k] = c;
         }
         else {
-#pragma unroll
-            for (int g = 0; g < NV; ++g) {
-                const V t = regs[(x * NV + g) * kFusedThreads + tid];
-#pragma unroll
-                for (int j = 0; j < VW; ++j) v[g * VW + j] = t.v[j];
-            }
+            load_reg(static_cast<int>(x) * NV, v);
         }
     };
 
-    for (int pc = 0; pc < prm.n_instr; ++pc) {
-        const uint64_t w = prm.code[pc];
-        const int op = static_cast<int>(w & 0xff);
-        const unsigned dst = static_cast<unsigned>((w >> 8) & 0xff);
-        const unsigned oa = static_cast<unsigned>((w >> 16) & 0xff);
-        const unsigned ob = static_cast<unsigned>((w >> 24) & 0xff);
-        const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
-        const bool swap = (w >> 40) & 1;
-        if (op == DPB_FUSED_LOAD) {
-            load_input(oa, acc);
+    for (int pc = 0; pc < prm.n_uop; ++pc) {
+        const FusedUop u = prm.uop[pc];
+        const int kind = u.kind_op & 0xff;
+        const int op = (u.kind_op >> 8) & 0xff;
+        const bool swap = (u.kind_op >> 16) & 1;
+        switch (kind) {
+        case FK_MOVE_REG: load_reg(u.b_off, acc); break;
+        case FK_MOVE_IMM: {
+            const T c = static_cast<T>(prm.imm[u.aux]);
+#pragma unroll
+            for (int k = 0; k < K; ++k) acc[k] = c;
+            break;
         }
-        else if (op == DPB_FUSED_STORE) {
-            T *dstp = static_cast<T *>(prm.out[ob]);
+        case FK_MOVE_IN: load_input(u.aux, acc); break;
+        case FK_STORE: store_out(u.aux, acc); break;
+        case FK_STORE_ANY: {
             T v[K];
-            fetch(oa, v);
-            if (whole && prm.vector_io) {
-#pragma unroll
-                for (int k = 0; k < K; k += VW) {
-                    V x;
-#pragma unroll
-                    for (int j = 0; j < VW; ++j) x.v[j] = v[k + j];
-                    store_vec(dstp + base + k, x);
-                }
-            }
-            else {
-#pragma unroll
-                for (int k = 0; k < K; ++k)
-                    if (base + k < n) dstp[base + k] = v[k];
-            }
-            continue;  // a store leaves the accumulator as it is
+            fetch_any(static_cast<unsigned>(u.b_off), v);
+            store_out(u.aux, v);
+            break;
         }
-        else if (op == DPB_FUSED_SELECT) {
+        case FK_SELECT: {
             T c[K], a[K], b[K];
-            fetch(oa, c);
-            fetch(ob, a);
-            fetch(oc, b);
+            fetch_any(static_cast<unsigned>(u.b_off & 0xff), c);
+            fetch_any(static_cast<unsigned>((u.b_off >> 8) & 0xff), a);
+            fetch_any(static_cast<unsigned>((u.b_off >> 16) & 0xff), b);
 #pragma unroll
             for (int k = 0; k < K; ++k) acc[k] = (c[k] != T(0)) ? a[k] : b[k];
+            break;
         }
-        else if (op < DPB_FUSED_FIRST_BINARY) {
-            if (oa != kOpndAcc) fetch(oa, acc);
-            fused_unary<T, K>(op, acc);
+        case FK_UNARY: fused_unary<T, K>(op, acc); break;
+        case FK_BIN_IMM: {
+            const T c = static_cast<T>(prm.imm[u.aux]);
+            if (swap) fused_binary_scalar<T, K, true>(op, acc, c);
+            else fused_binary_scalar<T, K, false>(op, acc, c);
+            break;
         }
-        else {
-            // the accumulator takes the first operand (or already holds it); a second operand
-            // that is the accumulator is saved first
+        default: {  // FK_BIN_REG, FK_BIN_IN, FK_BIN_ACC
             T b[K];
-            fetch(ob, b);
-            if (oa != kOpndAcc) fetch(oa, acc);
+            if (kind == FK_BIN_REG) load_reg(u.b_off, b);
+            else if (kind == FK_BIN_IN) load_input(u.aux, b);
+            else {
+#pragma unroll
+                for (int k = 0; k < K; ++k) b[k] = acc[k];
+            }
             if (swap) fused_binary<T, K, true>(op, acc, b);
             else fused_binary<T, K, false>(op, acc, b);
+            break;
         }
-        if (dst != kNoDst) {
+        }
+        if (u.dst_off >= 0) {
 #pragma unroll
             for (int g = 0; g < NV; ++g) {
                 V t;
 #pragma unroll
                 for (int j = 0; j < VW; ++j) t.v[j] = acc[g * VW + j];
-                regs[(dst * NV + g) * kFusedThreads + tid] = t;
+                regs[(u.dst_off + g) * kFusedThreads + tid] = t;
             }
         }
     }
@@ -272,7 +349,6 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
     if (n < 0) return set_error(DPB_ERR_VALUE, "negative element count");
     FusedParams prm;
     std::memset(&prm, 0, sizeof(prm));
-    prm.n_instr = prog->n_instr;
     bool aligned = true;
     for (int i = 0; i < prog->n_in; ++i) {
         if (!prog->in[i]) return set_error(DPB_ERR_VALUE, "fused program: null input pointer");
@@ -308,11 +384,64 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
             ok = operand_ok(oa, prog->n_reg, prog->n_imm, prog->n_in, first) && operand_ok(ob, prog->n_reg, prog->n_imm, prog->n_in, first);
         if (ok && op != DPB_FUSED_STORE) ok = dst == kNoDst || static_cast<int>(dst) < prog->n_reg;
         if (!ok) return set_error(DPB_ERR_VALUE, "fused program: malformed instruction");
-        prm.code[pc] = w;
     }
     if (n == 0 || prog->n_instr == 0) return DPB_OK;
     const size_t elem = prog->typenum == DPB_DOUBLE ? 8 : 4;
     const int K = static_cast<int>(tuning_fused_elems());
+    // ---- instruction words -> micro-operations
+    const int NV = K / static_cast<int>(16 / elem);     // 16-byte groups per thread and register
+    int nu = 0;
+    auto emit = [&](int kind, int op, bool swap, int dst_off, int b_off, int aux) {
+        prm.uop[nu].kind_op = kind | (op << 8) | ((swap ? 1 : 0) << 16);
+        prm.uop[nu].dst_off = dst_off;
+        prm.uop[nu].b_off = b_off;
+        prm.uop[nu].aux = aux;
+        ++nu;
+    };
+    // acc <- operand x (which is not the accumulator)
+    auto emit_move = [&](unsigned x, int dst_off) {
+        if (x >= kOpndIn) emit(FK_MOVE_IN, 0, false, dst_off, 0, static_cast<int>(x - kOpndIn));
+        else if (x >= kOpndImm) emit(FK_MOVE_IMM, 0, false, dst_off, 0, static_cast<int>(x - kOpndImm));
+        else emit(FK_MOVE_REG, 0, false, dst_off, static_cast<int>(x) * NV, 0);
+    };
+    for (int pc = 0; pc < prog->n_instr; ++pc) {
+        const uint64_t w = prog->code[pc];
+        const int op = static_cast<int>(w & 0xff);
+        const unsigned dst = static_cast<unsigned>((w >> 8) & 0xff);
+        unsigned oa = static_cast<unsigned>((w >> 16) & 0xff);
+        unsigned ob = static_cast<unsigned>((w >> 24) & 0xff);
+        const unsigned oc = static_cast<unsigned>((w >> 32) & 0xff);
+        bool swap = (w >> 40) & 1;
+        const int dst_off = (dst == kNoDst || op == DPB_FUSED_STORE) ? -1 : static_cast<int>(dst) * NV;
+        if (op == DPB_FUSED_LOAD) {
+            emit(FK_MOVE_IN, 0, false, dst_off, 0, static_cast<int>(oa));
+        }
+        else if (op == DPB_FUSED_STORE) {
+            if (oa == kOpndAcc) emit(FK_STORE, 0, false, -1, 0, static_cast<int>(ob));
+            else emit(FK_STORE_ANY, 0, false, -1, static_cast<int>(oa), static_cast<int>(ob));
+        }
+        else if (op == DPB_FUSED_SELECT) {
+            emit(FK_SELECT, 0, false, dst_off, static_cast<int>(oa | (ob << 8) | (oc << 16)), 0);
+        }
+        else if (op < DPB_FUSED_FIRST_BINARY) {
+            if (oa != kOpndAcc) emit_move(oa, -1);
+            emit(FK_UNARY, op, false, dst_off, 0, 0);
+        }
+        else {
+            if (oa != kOpndAcc && ob == kOpndAcc) {   // give the accumulator as the first operand
+                const unsigned t = oa;
+                oa = ob;
+                ob = t;
+                swap = !swap;
+            }
+            if (oa != kOpndAcc) emit_move(oa, -1);
+            if (ob == kOpndAcc) emit(FK_BIN_ACC, op, swap, dst_off, 0, 0);
+            else if (ob >= kOpndIn) emit(FK_BIN_IN, op, swap, dst_off, 0, static_cast<int>(ob - kOpndIn));
+            else if (ob >= kOpndImm) emit(FK_BIN_IMM, op, swap, dst_off, 0, static_cast<int>(ob - kOpndImm));
+            else emit(FK_BIN_REG, op, swap, dst_off, static_cast<int>(ob) * NV, 0);
+        }
+    }
+    prm.n_uop = nu;
     const size_t smem = static_cast<size_t>(prog->n_reg > 0 ? prog->n_reg : 1) * K * kFusedThreads * elem;
     if (smem > device_props().max_smem_optin)
         return set_error(DPB_ERR_VALUE, "fused program: %d registers do not fit in shared memory", prog->n_reg);
