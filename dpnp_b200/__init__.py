@@ -30,7 +30,7 @@ from ._ufuncs import (acos, acosh, angle, arccos, arccosh, arcsin, arcsinh, arct
                       bitwise_not, bitwise_or, bitwise_right_shift, bitwise_xor, cbrt, conj, conjugate,
                       copysign, cosh, exp2, fix, floor_divide, hypot, imag, invert, left_shift, log2,
                       log10, logaddexp, logical_xor, mod, nextafter, proj, real, remainder, right_shift,
-                      rint, rsqrt, signbit, sinh, tan, trunc)
+                      rint, round, around, rsqrt, signbit, sinh, tan, trunc)
 from .dpnp_array import dpnp_array
 from .dpnp_array import dpnp_array as ndarray
 from .memory import ExecutionPlacementError, StreamQueue, get_default_queue

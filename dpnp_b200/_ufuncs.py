@@ -208,3 +208,33 @@ right_shift = bitwise_right_shift = DPNPBinaryFunc(ef.bitwise_right_shift, "righ
 floor_divide = DPNPBinaryFunc(ef.floor_divide)
 remainder = mod = DPNPBinaryFunc(ef.remainder)
 logical_xor = DPNPBinaryFunc(ef.logical_xor)
+
+
+class DPNPRound(DPNPUnaryFunc):
+    """dpnp.round / dpnp.around: rounding to `decimals` places by scaling, rounding half to even
+    and scaling back (dpnp/dpnp_algo/dpnp_elementwise_common.py:1290-1341)."""
+
+    def __call__(self, x, /, decimals=0, out=None, *, dtype=None):
+        if decimals == 0:
+            return super().__call__(x, out=out, dtype=dtype)
+        x_usm = _usm(x)
+        out = _unpack_out(out)
+        out_usm = None if out is None else _usm(out)
+        if x_usm.dtype.kind in "iu":
+            if decimals < 0:
+                dtype = x_usm.dtype
+                x_usm = ef.round(x_usm * 10 ** decimals, out=out_usm)
+                res_usm = ef.divide(x_usm, 10 ** decimals, out=out_usm)
+            else:
+                res_usm = ef.round(x_usm, out=out_usm)
+        else:
+            x_usm = ef.round(x_usm * 10 ** decimals, out=out_usm)
+            res_usm = ef.divide(x_usm, 10 ** decimals, out=out_usm)
+        if dtype is not None:
+            res_usm = dpt.astype(res_usm, dtype, copy=False)
+        if out is not None and isinstance(out, dpnp_array):
+            return out
+        return dpnp_array._create_from_usm_ndarray(res_usm)
+
+
+round = around = DPNPRound(ef.round, "round")

@@ -109,6 +109,21 @@ def test_rounding_sign_and_complex_parts_are_exact(dt):
         assert ef.trunc.result_type_resolver_fn_(np.dtype(dt)) is None
 
 
+def test_round_with_decimals():
+    """dpnp.round scales, rounds half to even and scales back (dpnp_elementwise_common.py:1317-1341)."""
+    import dpnp_b200 as dp
+
+    x = np.array([1.2345, -2.5, 0.125, 37.5, 1234.5678])
+    np.testing.assert_allclose(dp.round(dev(x), 2).asnumpy(), np.round(x, 2), rtol=1e-15)
+    np.testing.assert_allclose(dp.around(dev(x), -1).asnumpy(), np.round(x, -1), rtol=1e-15)
+    np.testing.assert_array_equal(dp.round(dev(x)).asnumpy(), np.round(x))
+    xi = np.array([14, 15, 25, -35, 123], dtype="i4")
+    np.testing.assert_array_equal(dp.round(dev(xi), 1).asnumpy(), xi)
+    out = dp.empty(5)
+    assert dp.round(dev(x), 1, out=out) is out
+    np.testing.assert_allclose(out.asnumpy(), np.round(x, 1), rtol=1e-15)
+
+
 def test_bool_inputs_of_round_conj_and_invert():
     import dpnp_b200 as dp
     from dpnp_b200.tensor import _elementwise_funcs as ef
