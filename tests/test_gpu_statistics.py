@@ -101,3 +101,67 @@ def test_logsumexp_and_reduce_hypot(dt):
     with pytest.raises(ValueError):
         dp.logsumexp(dev(np.ones(3, "c8")))
     assert dp.logsumexp(d, axis=0, dtype="f8").dtype == np.dtype("f8")
+
+
+# ---- known-answer cases of the reference's own tests
+def test_reference_var_std_literals():
+    """dpnp/tests/tensor/test_tensor_statistical_functions.py:176-230."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    x = dev(np.arange(9, dtype="f4").reshape(3, 3)).get_array()
+    g = lambda r: dp.asnumpy(r)
+    np.testing.assert_allclose(g(dpt.var(x)), np.float32(6.666666507720947), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.var(x, correction=3)), np.float32(10.0), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.std(x)), np.sqrt(np.float32(6.666666507720947)), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.std(x, correction=3)), np.sqrt(np.float32(10.0)), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.var(x, axis=0)), np.full(3, 6, "f4"), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.var(x, axis=0, correction=1)), np.full(3, 9, "f4"), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.std(x, axis=0)), np.sqrt(np.full(3, 6, "f4")), rtol=1e-6)
+    np.testing.assert_allclose(g(dpt.var(x, axis=1)), np.full(3, 0.6666666865348816, "f4"), rtol=1e-6)
+    assert dpt.var(x).dtype == np.dtype("f4") and dpt.var(x).shape == ()
+
+
+def test_reference_logsumexp_hypot_count_nonzero_cases():
+    """dpnp/tests/tensor/test_usm_ndarray_reductions.py:321-436 (logsumexp), :445-470 (reduce_hypot),
+    :690-705 (count_nonzero)."""
+    import dpnp_b200 as dp
+
+    dpt = dp.tensor
+    for dt in ("?", "i1", "u1", "i2", "u2", "i4", "u4", "i8", "u8", "f2", "f4", "f8"):
+        m = dp.ones(100, dtype=dt).get_array()
+        r = dpt.logsumexp(m)
+        assert r.dtype.kind == "f"
+        tol = np.finfo(r.dtype).resolution
+        # closed form 1 + log(100) (the reference compares with NumPy's sequential reduction in the
+        # result type, which for float16 is itself 1.4e-3 away from the exact value)
+        np.testing.assert_allclose(float(dp.asnumpy(r)), 1 + np.log(100.0), rtol=tol, atol=tol)
+        h = dpt.reduce_hypot(m)
+        assert h.dtype.kind == "f"
+        np.testing.assert_allclose(float(dp.asnumpy(h)), 10.0, rtol=tol, atol=tol)
+    y = dpt.logsumexp(dp.empty((0,), dtype="f4").get_array())
+    assert y.shape == () and dp.asnumpy(y) == -np.inf
+    y = dpt.reduce_hypot(dp.empty((0,), dtype="f4").get_array())
+    assert y.shape == () and dp.asnumpy(y) == 0
+    m = dp.ones((3, 4, 5, 6, 7), dtype="f4").get_array()
+    s = dpt.logsumexp(m, axis=(1, 2, -1))
+    assert s.shape == (3, 6)
+    np.testing.assert_allclose(dp.asnumpy(s), np.full((3, 6), np.log(140.0) + 1, "f4"), rtol=1e-6)
+    mi = dp.ones((3, 4, 5, 6, 7), dtype="i4").get_array()
+    assert dpt.logsumexp(mi, axis=(1, 2, -1), keepdims=True).shape == (3, 1, 1, 6, 1)
+    a = dp.ones((10, 0, 10)).get_array()
+    assert dpt.logsumexp(a, keepdims=True).shape == (1, 1, 1)
+    assert dpt.logsumexp(a, axis=(0, 1), keepdims=True).shape == (1, 1, 10)
+    assert dpt.logsumexp(a, axis=(1, 2), keepdims=True).shape == (10, 1, 1)
+    assert dpt.logsumexp(a, axis=(0, 2), keepdims=True).shape == (1, 0, 1)
+    assert dpt.logsumexp(a[0], keepdims=True).shape == (1, 1)
+    assert dpt.logsumexp(dp.ones(()).get_array()).shape == ()
+    with pytest.raises(ValueError):
+        dpt.logsumexp(dp.zeros(1, dtype="c8").get_array())
+    assert dpt.logsumexp(dp.zeros((8, 10), dtype="f4").get_array(), axis=0).shape == (10,)
+    for dt in ("?", "i1", "u1", "i2", "u2", "i4", "u4", "i8", "u8", "f2", "f4", "f8", "c8", "c16"):
+        x = dp.ones(10, dtype=dt)
+        r = dpt.count_nonzero(x.get_array())
+        assert int(dp.asnumpy(r)) == 10 and r.dtype == np.dtype("i8")
+        x[3:6] = 0
+        assert int(dp.asnumpy(dpt.count_nonzero(x.get_array()))) == 7
