@@ -143,7 +143,7 @@ template <template <class, class> class Red, bool FP_ONLY, int TI, int TO> void 
 {
     using I = type_of_t<TI>;
     using O = type_of_t<TO>;
-    if constexpr (FP_ONLY ? fp_pair_v<I, O> : (accumulate_pair_v<I, O> && !is_cplx_v<I>))
+    if constexpr (FP_ONLY ? fp_pair_v<I, O> : accumulate_pair_v<I, O>)
         tab[TI][TO] = &scan_entry<Red<I, O>>;
 }
 template <template <class, class> class Red, bool FP_ONLY, int TI, int... TO>

@@ -207,3 +207,19 @@ def test_reference_nan_propagation_and_type_matrix():
             r = dpt.cumulative_sum(m, dtype=out)
             assert r.dtype == np.dtype(out)
             np.testing.assert_array_equal(dp.asnumpy(r), np.arange(1, 101).astype(out))
+
+
+def test_complex_running_sums_and_products():
+    import dpnp_b200 as dp
+
+    rng = np.random.default_rng(21)
+    for dt, tol in (("c8", 2e-5), ("c16", 1e-12)):
+        x = (rng.normal(0, 1, (6, 3000)) + 1j * rng.normal(0, 1, (6, 3000))).astype(dt)
+        for ax in (0, 1):
+            got = dp.cumsum(dev(x), axis=ax)
+            assert got.dtype == np.dtype(dt)
+            ref = np.cumsum(x.astype("c16"), axis=ax)
+            mag = np.cumsum(np.abs(x).astype("f8"), axis=ax)
+            assert np.all(np.abs(got.asnumpy() - ref) <= tol * mag + 1e-30)
+        u = np.exp(1j * rng.uniform(0, 6.28, 200)).astype(dt)          # unit modulus: products stay bounded
+        np.testing.assert_allclose(dp.cumprod(dev(u)).asnumpy(), np.cumprod(u.astype("c16")), rtol=tol * 300, atol=tol * 300)
