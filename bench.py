@@ -547,6 +547,17 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     ms = median_time_ms(ev, lambda: dp.multiply(xv, 2.0, out=xw), 10, batch=8)
     rec("sliced_rows_multiply_f64_16384x4094", 16 * mrows * (mcols - 2) * world, ms,
         note="rows start off the 16-byte grid")
+    xcol = xb[:mrows].reshape(mrows, 1)
+    ms = median_time_ms(ev, lambda: dp.subtract(xm, xcol, out=xom), 10, batch=8)
+    rec("col_broadcast_subtract_f64_16384x4096", 16 * ne * world, ms, note="matrix minus column vector")
+    xt_src = xa.reshape(4096, 16384)
+    ms = median_time_ms(ev, lambda: dp.copyto(xom, xt_src.T), 10, batch=8)
+    rec("copy_transposed_f64_16384x4096", 16 * ne * world, ms, note="layout-changing copy (a.T into a C-ordered array)")
+    xs2 = xa.reshape(mrows, mcols)[:, ::2]
+    xo2 = xo.reshape(mrows, mcols)[:, : mcols // 2]
+    ms = median_time_ms(ev, lambda: dp.multiply(xs2, 2.0, out=xo2), 10, batch=8)
+    rec("inner_stride2_multiply_f64_16384x2048", 16 * mrows * (mcols // 2) * world, ms,
+        note="input with inner stride 2: every 32-byte sector is half used (algorithmic bytes counted)")
     x3 = xa.reshape(64, 1024, 1024)
     ms = median_time_ms(ev, lambda: dp.sum(x3, axis=1), 10, batch=8)
     rec("sum_middle_axis_f64_64x1024x1024", 8 * ne * world, ms)
