@@ -243,6 +243,52 @@ __global__ void __launch_bounds__(kEwThreads, 5)
                 }
                 continue;
             }
+            else {
+                // the chunk that holds the end of the row: the same two phases, every vector
+                // guarded, the one ragged vector element by element
+                vec_t<In0, VEC> va[S0 ? UNROLL : 1];
+                vec_t<In1, VEC> vb[S1 ? UNROLL : 1];
+                vec_t<In2, VEC> vc[S2 ? UNROLL : 1];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int64_t j = (v0 + int64_t(u) * TX) * VEC;
+                    if (j + VEC <= Lb) {
+                        if constexpr (S0) va[u] = load_vec<vec_t<In0, VEC>>(a + j);
+                        if constexpr (S1) vb[u] = load_vec<vec_t<In1, VEC>>(b + j);
+                        if constexpr (S2) vc[u] = load_vec<vec_t<In2, VEC>>(c + j);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int64_t j = (v0 + int64_t(u) * TX) * VEC;
+                    if (j + VEC <= Lb) {
+                        vec_t<Out, VEC> r;
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) {
+                            In0 x = sa;
+                            In1 y = sb;
+                            In2 z = sc;
+                            if constexpr (S0) x = va[u].v[k];
+                            if constexpr (S1) y = vb[u].v[k];
+                            if constexpr (S2) z = vc[u].v[k];
+                            r.v[k] = ew_apply(f, x, y, z);
+                        }
+                        store_vec(o + j, r);
+                    }
+                    else {
+                        for (int64_t e = j; e < Lb; ++e) {
+                            In0 x = sa;
+                            In1 y = sb;
+                            In2 z = sc;
+                            if constexpr (S0) x = a[e];
+                            if constexpr (S1) y = b[e];
+                            if constexpr (S2) z = c[e];
+                            o[e] = ew_apply(f, x, y, z);
+                        }
+                    }
+                }
+                continue;
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
