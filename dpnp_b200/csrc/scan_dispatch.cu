@@ -66,10 +66,10 @@ template <class R> int launch_scan(const ScanPlan &plan, const void *vsrc, void 
         (plan.s_src != 1 || plan.s_dst != 1)) {
         const int64_t cols = plan.iter_shape[last];
         const int64_t nbatch = nrows / cols;
-        if (cols >= 32 && nbatch * ceil_div(cols, kScanThreads) >= int64_t(device_props().sm_count)) {
+        if (cols >= 32 && nbatch * ceil_div(cols, 256) >= int64_t(device_props().sm_count)) {
             RedMeta batch = make_meta(last, plan.iter_shape, plan.iter_src, plan.iter_dst);
-            const int64_t nwork = nbatch * ceil_div(cols, kScanThreads);
-            scan_cols_kernel<R><<<static_cast<int>(std::min<int64_t>(nwork, int64_t(1) << 30)), kScanThreads, 0,
+            const int64_t nwork = nbatch * ceil_div(cols, kScanColThreads);
+            scan_cols_kernel<R><<<static_cast<int>(std::min<int64_t>(nwork, int64_t(1) << 30)), kScanColThreads, 0,
                                   stream>>>(src, dst, batch, nbatch, cols, L, plan.s_src, plan.s_dst,
                                             plan.dst_shift);
             note_kernel("scan_cols");

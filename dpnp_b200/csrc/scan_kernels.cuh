@@ -23,6 +23,9 @@
 namespace dpb {
 
 constexpr int kScanThreads = 256;
+// column scans use small blocks: all of them are resident at once for the sizes that take this
+// path, and many small blocks spread evenly over the SMs where a few large ones would not
+constexpr int kScanColThreads = 64;
 
 template <class T> DPB_D T shfl_idx_any(const T &v, int src_lane)
 {
@@ -197,17 +200,17 @@ __global__ void __launch_bounds__(kScanThreads)
 // `cols` columns are unit-stride in src and dst; a thread owns one column of one batch entry
 // and walks the L rows (stride r_src / r_dst) with 8 to 32 loads in flight.
 template <class R>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanColThreads)
     scan_cols_kernel(const typename R::In *src, typename R::Out *dst, RedMeta batch, int64_t nbatch,
                      int64_t cols, int64_t L, int64_t r_src, int64_t r_dst, int64_t dst_shift)
 {
     using In = typename R::In;
     using Acc = typename R::Acc;
-    const int64_t colblocks = (cols + kScanThreads - 1) / kScanThreads;
+    const int64_t colblocks = (cols + kScanColThreads - 1) / kScanColThreads;
     const int64_t nwork = nbatch * colblocks;
     for (int64_t w = blockIdx.x; w < nwork; w += gridDim.x) {
         const int64_t b = w / colblocks;
-        const int64_t c = (w - b * colblocks) * kScanThreads + threadIdx.x;
+        const int64_t c = (w - b * colblocks) * kScanColThreads + threadIdx.x;
         if (c >= cols) continue;
         int64_t o_src, o_dst;
         red_offsets(batch, b, o_src, o_dst);
