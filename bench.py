@@ -673,7 +673,7 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     return out
 
 
-PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "fuse_cheap", "rows_bcast",
+PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "fuse_cheap", "cumsum_axis1", "cumsum_flat", "generic_stride2", "rows_bcast",
                  "argmax_axis0", "sum_axis1",
                  "sum_axis0", "mean_all", "transpose_c4", "max_i32", "argmax_i32")
 
@@ -720,6 +720,18 @@ def profile_case(name, launches=3):
             o_[:] = v
         chain = dp.fuse(cheap)
         fn = lambda: chain(x, o)
+    elif name in ("cumsum_axis1", "cumsum_flat"):
+        x = dp.random.normal(0, 1, (4096, 65536), dtype="f4")
+        o = dp.empty((4096, 65536), dtype="f4")
+        if name == "cumsum_axis1":
+            fn = lambda: dp.cumsum(x, axis=1, out=o)
+        else:
+            xf, of = x.reshape(-1), o.reshape(-1)
+            fn = lambda: dp.cumsum(xf, out=of)
+    elif name == "generic_stride2":
+        x, o = dp.random.uniform(-1, 1, (8192, 4096)), dp.empty((8192, 2048))
+        xs = x[:, ::2]
+        fn = lambda: dp.multiply(xs, 2.0, out=o)
     elif name == "rows_bcast":
         x, r, o = dp.random.uniform(-1, 1, (8192, 4096)), dp.random.uniform(-1, 1, 4096), dp.empty((8192, 4096))
         fn = lambda: dp.subtract(x, r, out=o)
