@@ -371,23 +371,24 @@ def run_gpu_arm(args):
     hp[1].array[:] = rng.uniform(10, 50, n)
     hp[2].array[:] = rng.uniform(1, 2, n)
 
-    # The batch is cut into chunks that rotate over three in-order queues: the copies of one chunk
+    # The batch is cut into chunks that rotate over a few in-order queues (3 by default; 4 or 6 measure the same): the copies of one chunk
     # overlap the chain of another and PCIe runs in both directions at once.  All work of one chunk
     # stays on one queue, as the API requires.
     from dpnp_b200.memory import StreamQueue
 
     nchunks = args.e2e_chunks
     csz = n // nchunks
-    queues = [StreamQueue(local_rank) for _ in range(3)]
+    nq = args.e2e_queues
+    queues = [StreamQueue(local_rank) for _ in range(nq)]
     chunk_bufs = []
-    for k in range(3):
+    for k in range(nq):
         qk = queues[k]
         chunk_bufs.append([dp.empty(csz, dtype=dp.float64, sycl_queue=qk) for _ in range(5)])
 
     def e2e_step():
         for ci in range(nchunks):
-            qk = queues[ci % 3]
-            cp, cs, ct, cc, cu = chunk_bufs[ci % 3]
+            qk = queues[ci % nq]
+            cp, cs, ct, cc, cu = chunk_bufs[ci % nq]
             lo, hi = ci * csz, (ci + 1) * csz
             for dst, src in zip((cp, cs, ct), hp):
                 memory.copy_host_to_device(dst, src.array[lo:hi], qk)
@@ -409,7 +410,7 @@ def run_gpu_arm(args):
     e2e_ms = max_over_ranks(e2e_wall_ms)
     e2e = {"value": world * n * BYTES_PER_OPTION_CHAIN / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": 3 * 8 * n, "d2h_bytes_per_step": 2 * 8 * n, "ms_per_step": e2e_ms,
-           "wall_ms_per_step": e2e_wall_ms, "steps": e2e_steps, "chunks": nchunks, "queues": 3,
+           "wall_ms_per_step": e2e_wall_ms, "steps": e2e_steps, "chunks": nchunks, "queues": nq,
            "checksum": float(ho[0].array[:1024].sum() + ho[1].array[:1024].sum())}
     del chunk_bufs
     for b in hp + ho:
@@ -768,6 +769,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-configuration extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-queues", type=int, default=3,
+                    help="in-order queues the chunks of the end-to-end measurement rotate over")
     ap.add_argument("--e2e-chunks", type=int, default=16,
                     help="pieces the batch is cut into for the pipelined end-to-end measurement")
     ap.add_argument("--profile-case", default=None, help="run one small case for an ncu capture: "
