@@ -183,3 +183,65 @@ def test_c_abi_rejects_malformed_programs():
         assert "malformed" in _lib.last_error()
     assert run(good, n_imm=1, typenum=5) == _lib.ERR_TYPE
     assert run(good, n_reg=25, n_imm=1) == _lib.ERR_VALUE
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_chains_fused_equal_op_by_op(seed):
+    """Random expression graphs (shared subexpressions, scalars on either side, comparisons
+    feeding where, stores into arguments): the interpreter must give the bits of the same
+    graph evaluated one kernel per operation."""
+    import dpnp_b200 as dp
+
+    rng = np.random.default_rng(500 + seed)
+    dt = "f8" if seed % 2 else "f4"
+    n_in, n_ops = int(rng.integers(1, 5)), int(rng.integers(4, 70))
+    un = ["negative", "abs", "square", "sin", "cos", "tanh", "floor", "ceil", "sign", "exp", "sqrt", "log1p", "erf"]
+    bi = ["add", "subtract", "multiply", "divide", "maximum", "minimum"]
+    plan = []
+    for k in range(n_ops):
+        r = rng.random()
+        if r < 0.3:
+            plan.append(("u", un[rng.integers(len(un))], int(rng.integers(0, n_in + k))))
+        elif r < 0.5:
+            plan.append(("s", bi[rng.integers(len(bi))], int(rng.integers(0, n_in + k)),
+                         float(np.round(rng.normal(), 2)) or 0.5, bool(rng.integers(2))))
+        elif r < 0.6:
+            plan.append(("w", int(rng.integers(0, n_in + k)), int(rng.integers(0, n_in + k)),
+                         int(rng.integers(0, n_in + k)), float(np.round(rng.normal(), 1))))
+        else:
+            plan.append(("b", bi[rng.integers(len(bi))], int(rng.integers(0, n_in + k)),
+                         int(rng.integers(0, n_in + k))))
+    picks = [int(v) for v in rng.integers(n_in, n_in + n_ops, int(rng.integers(1, 4)))]
+    store_into = int(rng.integers(0, n_in)) if rng.random() < 0.5 else None
+
+    def chain(*arrays):
+        vals = list(arrays)
+        for p in plan:
+            if p[0] == "u":
+                vals.append(getattr(dp, p[1])(vals[p[2]]))
+            elif p[0] == "s":
+                f = getattr(dp, p[1])
+                vals.append(f(p[3], vals[p[2]]) if p[4] else f(vals[p[2]], p[3]))
+            elif p[0] == "w":
+                vals.append(dp.where(vals[p[1]] > p[4], vals[p[2]], vals[p[3]]))
+            else:
+                vals.append(getattr(dp, p[1])(vals[p[2]], vals[p[3]]))
+        if store_into is not None:
+            arrays[store_into][:] = vals[picks[0]]
+        return tuple(vals[i] for i in picks)
+
+    n = int(rng.choice([1000, 4099, 1 << 16]))
+    host = [rng.normal(0, 2, n).astype(dt) for _ in range(n_in)]
+    a0, a1 = [dp.asarray(h) for h in host], [dp.asarray(h) for h in host]
+    with np.errstate(all="ignore"):
+        ref = chain(*a0)
+        fused = dp.fuse(chain)
+        got = fused(*a1)
+    if fused.fused_calls == 0:
+        assert "limits" in fused.last_reason or "register" in fused.last_reason, fused.last_reason
+        return
+    ut = "u8" if dt == "f8" else "u4"
+    for g, r in zip(got, ref):
+        np.testing.assert_array_equal(g.asnumpy().view(ut), r.asnumpy().view(ut))
+    for u, v in zip(a0, a1):
+        np.testing.assert_array_equal(u.asnumpy().view(ut), v.asnumpy().view(ut))
