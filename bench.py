@@ -656,12 +656,9 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
         return sharded.allreduce_extreme(part, "max") if dist is not None else part
 
     def c5_argmax():
-        idx = dp.argmax(x)
         if dist is None:
-            return idx
-        i_loc = int(idx.asnumpy())
-        v = x.reshape(-1)[i_loc].asnumpy()
-        return sharded.combine_arg_extreme(v, i_loc + rank * r5 * (1 << 29), "max")
+            return dp.argmax(x)
+        return sharded.arg_extreme_sharded(x, rank * r5 * (1 << 29), "max")
 
     ms = time_sharded(c5_max, 5)
     rec("c5_max_flat_int32_8x2^29", nb, ms)
@@ -669,6 +666,14 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, dist, sharded, price, stri
     rec("c5_max_lastaxis_int32_8x2^29", nb, ms)
     ms = time_sharded(c5_argmax, 5)
     rec("c5_argmax_flat_int32_8x2^29", nb, ms)
+    if dist is not None:
+        # the combined (value, index) against the combined maximum, and the index against its owner
+        v, gi = c5_argmax()
+        vmax = int(sharded.allreduce_extreme(dp.max(x), "max").asnumpy())
+        owner, local = divmod(int(gi), r5 * (1 << 29))
+        mine = int(x.reshape(-1)[local].asnumpy()) if owner == rank else vmax
+        if int(v) != vmax or mine != vmax:
+            raise RuntimeError("sharded argmax disagrees with the sharded maximum")
     ms = time_sharded(lambda: dp.argmax(x, axis=-1), 5)
     rec("c5_argmax_lastaxis_int32_8x2^29", nb, ms)
     return out

@@ -162,6 +162,7 @@ PROTOTYPES = {
     "dpb_random_normal": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),
     "dpb_linspace_step": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
     "dpb_linspace_affine": (_i, [_i, _vp, _i64, _vp, _vp, _i, _vp]),
+    "dpb_take_one": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
     "dpb_last_kernel": (C.c_char_p, []),
     "dpb_launch_count": (_i64, []),
     "dpb_reset_launch_count": (None, []),

@@ -115,3 +115,27 @@ extern "C" int dpb_linspace_affine(int typenum, void *dst, int64_t nelems, const
     note_kernel("sequence_affine");
     return check_launch("sequence_affine");
 }
+
+// dst[0] = src[index[0]] for an index held on the device (one element of `elem_size` bytes):
+// lets a search result be turned into (value, index) without a host round trip.
+namespace dpb {
+__global__ void take_one_kernel(const unsigned char *src, const int64_t *index, unsigned char *dst, int elem_size,
+                                int64_t nelems)
+{
+    int64_t i = index[0];
+    if (i < 0) i = 0;                 // the caller validates; never read outside the array
+    if (i >= nelems) i = nelems - 1;
+    if (threadIdx.x < elem_size) dst[threadIdx.x] = src[i * elem_size + threadIdx.x];
+}
+}  // namespace dpb
+
+extern "C" int dpb_take_one(int typenum, const void *src, int64_t nelems, const void *index, void *dst, void *stream)
+{
+    if (typenum < 0 || typenum >= DPB_NUM_TYPES) return set_error(DPB_ERR_VALUE, "unknown type id");
+    if (!src || !index || !dst || nelems <= 0) return set_error(DPB_ERR_VALUE, "null argument or empty array");
+    take_one_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned char *>(src), static_cast<const int64_t *>(index),
+        static_cast<unsigned char *>(dst), static_cast<int>(type_size(typenum)), nelems);
+    note_kernel("take_one");
+    return check_launch("take_one");
+}

@@ -144,3 +144,46 @@ def combine_arg_extreme(value, global_index, op="max", group=None):
         if better:
             best = r
     return v.dtype.type(pairs[best][0]), np.int64(pairs[best][1])
+
+
+def arg_extreme_sharded(x, index_offset, op="max", group=None):
+    """Global argmax/argmin of an array sharded along its leading axis: `x` is this rank's shard,
+    `index_offset` the flat index of its first element in the whole array.  The local search, the
+    read of the extreme value and both exchanges stay on the device and on the array's stream; the
+    host reads the gathered (value, index) pairs once and applies the first-occurrence rule.
+    Returns (value, index) as NumPy scalars."""
+    import ctypes as C
+
+    import dpnp_b200 as dp
+    from dpnp_b200._lib import check, lib, typenum_of
+
+    dist = _dist()
+    world = dist.get_world_size(group)
+    arr = x.get_array() if hasattr(x, "get_array") else x
+    if not arr.flags.c_contiguous:
+        raise ValueError("the shard must be C-contiguous")
+    q = arr.sycl_queue
+    idx = (dp.argmax if op == "max" else dp.argmin)(x)            # 0-d int64 on the device
+    idx_arr = idx.get_array() if hasattr(idx, "get_array") else idx
+    val = dp.empty((1,), dtype=arr.dtype, sycl_queue=q)
+    check(lib.dpb_take_one(typenum_of(arr.dtype), C.c_void_p(arr._ptr), arr.size, C.c_void_p(idx_arr._ptr),
+                           C.c_void_p(val.get_array()._ptr), C.c_void_p(q.stream)))
+    gidx = dp.add(dp.reshape(idx, (1,)), int(index_offset))          # global flat index
+    vals = dp.empty((world,), dtype=arr.dtype, sycl_queue=q)
+    idxs = dp.empty((world,), dtype="i8", sycl_queue=q)
+    with _on_queue_stream(arr):
+        dist.all_gather_into_tensor(_as_torch(vals.get_array()), _as_torch(val.get_array()), group=group)
+        dist.all_gather_into_tensor(_as_torch(idxs.get_array()), _as_torch(gidx.get_array()), group=group)
+    v, i = vals.asnumpy(), idxs.asnumpy()                            # the one host read
+    best = 0
+    for r in range(1, world):
+        a_nan, b_nan = v[r] != v[r], v[best] != v[best]
+        if a_nan or b_nan:
+            better = a_nan and (not b_nan or i[r] < i[best])
+        elif v[r] == v[best]:
+            better = i[r] < i[best]
+        else:
+            better = v[r] > v[best] if op == "max" else v[r] < v[best]
+        if better:
+            best = r
+    return v[best], np.int64(i[best])

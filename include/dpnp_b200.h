@@ -576,6 +576,12 @@ int dpb_linspace_step(int typenum, void *dst, int64_t nelems, const void *start,
 int dpb_linspace_affine(int typenum, void *dst, int64_t nelems, const void *start, const void *end,
                         int include_endpoint, void *stream);
 
+/* dst[0] = src[index[0]] with the int64 index read on the device (clamped to the array): turns the
+ * result of a flattened argmax/argmin into its value without a host round trip.  The reference
+ * reads such an element through usm_ndarray.__getitem__ and a device-to-host copy
+ * (dpnp/tensor/_usmarray.pyx: __getitem__, _copy_utils.py:_copy_to_numpy). */
+int dpb_take_one(int typenum, const void *src, int64_t nelems, const void *index, void *dst, void *stream);
+
 /* --------------------------------------------------------- introspection  */
 /* Name of the kernel family chosen by the most recent dispatch-level call in
  * this thread ("binary_contig_vec", "strided_rows", "transpose_tile", ...),
