@@ -357,6 +357,12 @@ class _Program:
             for c in children(j):
                 if nodes[c][0] == "in":
                     last_read[nodes[c][1]] = p_
+        # A store or result whose value is an argument itself (`c[:] = a`, `return +a`) reads that
+        # argument when the store runs, i.e. after every computation: it counts as a reader at `end`.
+        written = {bind[1] for bind in self.out_bind if bind[0] == "slot"}
+        for v, out_i in store_list:
+            if nodes[v][0] == "in" and self.out_bind[out_i] != ("slot", nodes[v][1]):
+                last_read[nodes[v][1]] = end
         eager, late = {}, []
         for v, out_i in store_list:
             bind = self.out_bind[out_i]
@@ -393,7 +399,8 @@ class _Program:
         for p, j in enumerate(order):
             k = nodes[j]
             # the result needs a register unless its single use is the very next instruction
-            only_next = (n_uses[j] == 1 and last_use[j] == p + 1) or (n_uses[j] == 0 and j in eager)
+            # (a value kept for a store at the end always gets one: last_use == end)
+            only_next = (n_uses[j] == 1 and last_use[j] == p + 1 < end) or (n_uses[j] == 0 and j in eager)
             if k[0] == "un":
                 word = (_OPS[k[1]], opnd(k[2], p, regs), 0, 0)
             elif k[0] == "bin":
@@ -424,8 +431,26 @@ class _Program:
             code.append(op | dst << 8 | a << 16 | b << 24 | c3 << 32)
             for out_i in eager.get(j, ()):             # stores do not disturb the accumulator
                 code.append(_OPS["store"] | _NO_DST << 8 | _OPND_ACC << 16 | out_i << 24)
+        # Late stores that copy an argument which another store overwrites (`a[:] = b; b[:] = t`,
+        # a swap) first move the old values into registers, so that the order of the stores
+        # does not matter.
+        saved = {}
         for v, out_i in late:
-            a = opnd(v, -1, regs) if nodes[v][0] in ("imm", "in") else regs[v]
+            if (nodes[v][0] == "in" and nodes[v][1] in written and v not in saved
+                    and self.out_bind[out_i] != ("slot", nodes[v][1])):
+                if free:
+                    free.sort()
+                    dst = free.pop(0)
+                else:
+                    dst = n_reg
+                    n_reg += 1
+                saved[v] = dst
+                code.append(_OPS["move"] | dst << 8 | opnd(v, -1, regs) << 16)
+        for v, out_i in late:
+            if v in saved and self.out_bind[out_i] != ("slot", nodes[v][1]):
+                a = saved[v]
+            else:
+                a = opnd(v, -1, regs) if nodes[v][0] in ("imm", "in") else regs[v]
             code.append(_OPS["store"] | _NO_DST << 8 | a << 16 | out_i << 24)
         if (len(code) > _MAX_INSTR or len(imms) > _MAX_IMM or len(self.in_slots) > _MAX_IN or
                 len(self.out_bind) > _MAX_OUT or n_reg > min(_MAX_REG, _OPND_IMM) or

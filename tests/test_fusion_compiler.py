@@ -33,6 +33,8 @@ def emulate(prog, inputs, n):
     dt = prog.dtype
     imm = [dt.type(v) for v in prog.imm[:max(1, prog.n_imm)]]
     regs, acc, outs = {}, None, {}
+    # stores into an argument change what later reads of that argument see, as on the device
+    inputs = [np.array(a, dtype=dt, copy=True) for a in inputs]
 
     def get(x, first):
         if x == 255:
@@ -54,6 +56,9 @@ def emulate(prog, inputs, n):
                     r = np.full(n, r.reshape(-1)[0], dt)
             elif op == "store":
                 outs[b] = get(a, first).copy()
+                bind = prog.out_bind[b]
+                if bind[0] == "slot" and bind[1] in prog.in_slots:
+                    inputs[prog.in_slots.index(bind[1])] = outs[b].reshape(inputs[prog.in_slots.index(bind[1])].shape)
                 continue
             elif op == "select":
                 r = np.where(get(a, first) != 0, get(b, first), get(c, first))
@@ -160,6 +165,39 @@ def test_read_then_write_of_the_same_argument_and_inplace_operators():
         if op == "store" and prog.out_bind[b][0] == "slot":
             code = 128 + prog.in_slots.index(prog.out_bind[b][1]) if prog.out_bind[b][1] in prog.in_slots else None
             assert all(code not in l[2:] for l in lst[i + 1:] if l[0] != "store")
+
+
+def test_stores_that_copy_an_argument_another_store_overwrites():
+    """A store whose value is an argument reads it when the store runs; a store into that
+    argument must not run first."""
+    def copy_then_overwrite(xp, a, b, c):
+        c[:] = a
+        a[:] = b * 2.0
+
+    def rotate(xp, a, b):
+        t = a + 0.0
+        a[:] = b
+        b[:] = t
+
+    def swap(xp, a, b):
+        ta, tb = +a, +b
+        a[:] = tb
+        b[:] = ta
+
+    def old_value_returned(xp, a, b):
+        t = +a
+        a[:] = b * 3.0
+        return t
+
+    rng = np.random.default_rng(8)
+    for chain, k in ((copy_then_overwrite, 3), (rotate, 2), (swap, 2), (old_value_returned, 2)):
+        arrays = [rng.normal(0, 1, 130) for _ in range(k)]
+        prog, outs, ref, ref_arrays = run_both(chain, arrays)
+        for i, bind in enumerate(prog.out_bind):
+            if bind[0] == "slot":
+                np.testing.assert_array_equal(outs[i], ref_arrays[bind[1]], err_msg=chain.__name__)
+            else:
+                np.testing.assert_array_equal(outs[i], ref, err_msg=chain.__name__)
 
 
 def test_size_one_arrays_broadcast_and_out_keyword():

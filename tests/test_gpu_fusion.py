@@ -122,6 +122,47 @@ def test_unaligned_starts_2d_shapes_scalar_arrays_and_aliases():
     assert g.fused_calls == 1
 
 
+def test_stores_that_copy_an_argument_another_store_overwrites():
+    """`c[:] = a; a[:] = ...`, a rotation through a temporary, a swap and an old value handed
+    back: the fused launch must leave what the op-by-op evaluation leaves."""
+    import dpnp_b200 as dp
+
+    def copy_then_overwrite(a, b, c):
+        c[:] = a
+        a[:] = b * 2.0
+
+    def rotate(a, b):
+        t = a + 0.0
+        a[:] = b
+        b[:] = t
+
+    def swap(a, b):
+        ta, tb = +a, +b
+        a[:] = tb
+        b[:] = ta
+
+    def old_value_returned(a, b):
+        t = +a
+        a[:] = b * 3.0
+        return t
+
+    rng = np.random.default_rng(21)
+    n = 5003
+    for chain, k in ((copy_then_overwrite, 3), (rotate, 2), (swap, 2), (old_value_returned, 2)):
+        host = [rng.normal(0, 1, n) for _ in range(k)]
+        # op by op on host copies defines the answer (plain assignments and IEEE-exact products)
+        want = [h.copy() for h in host]
+        want_res = chain(*want)
+        dev = [dp.asarray(h) for h in host]
+        fused = dp.fuse(chain)
+        got_res = fused(*dev)
+        assert fused.fused_calls == 1, (chain.__name__, fused.last_reason)
+        for d, w in zip(dev, want):
+            np.testing.assert_array_equal(d.asnumpy(), w, err_msg=chain.__name__)
+        if want_res is not None:
+            np.testing.assert_array_equal(got_res.asnumpy(), want_res, err_msg=chain.__name__)
+
+
 def test_calls_that_are_not_fused_run_op_by_op():
     import dpnp_b200 as dp
     from dpnp_b200 import _lib
