@@ -112,7 +112,39 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None,
     return LIB_PATH
 
 
+def shim_path() -> str:
+    import sysconfig
+
+    return os.path.join(HERE, "_tensor_native" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_shim(force: bool = False) -> str:
+    """Compile the pybind11 shim (csrc/pyshim/tensor_native.cpp) with the host compiler and link
+    it against libdpnp_b200.so, found at run time next to the module ($ORIGIN)."""
+    import sysconfig
+
+    import pybind11
+
+    src = os.path.join(CSRC, "pyshim", "tensor_native.cpp")
+    out = shim_path()
+    header = os.path.join(os.path.dirname(HERE), "include", "dpnp_b200.h")
+    if (not force and os.path.exists(out)
+            and os.path.getmtime(out) >= max(os.path.getmtime(src), os.path.getmtime(header),
+                                             os.path.getmtime(LIB_PATH))):
+        return out
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+           "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+           src, "-o", out, "-L", HERE, "-l:libdpnp_b200.so", "-Wl,-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("building the pybind11 shim failed")
+    return out
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
                  ptxas_info="--ptxas" in sys.argv)
     print(path)
+    print(build_shim(force="--force" in sys.argv))

@@ -179,6 +179,18 @@ for _name, (_res, _args) in PROTOTYPES.items():
     _fn.argtypes = _args
 
 
+# The pybind11 shim (csrc/pyshim/tensor_native.cpp) is the binding the hot calls go through: it
+# hands the library a `dpb_array` kept on each Python array and costs about a microsecond per
+# call.  ctypes above stays the binding of everything else, and of the hot calls too when the
+# shim has not been built (`native is None`); both reach the same library and the same kernels.
+try:
+    from . import _tensor_native as native
+except ImportError:
+    if os.environ.get("DPNP_B200_REQUIRE_NATIVE"):
+        raise
+    native = None
+
+
 def last_error() -> str:
     return lib.dpb_last_error().decode("utf-8", "replace")
 

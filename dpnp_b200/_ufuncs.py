@@ -52,6 +52,12 @@ def _norm_order(order):
     raise ValueError(f"order must be one of 'C', 'F', 'A', or 'K' (got '{order}')")
 
 
+def _wrap_new(usm_ary):
+    res = dpnp_array.__new__(dpnp_array)
+    res._array_obj = usm_ary
+    return res
+
+
 def _unpack_out(out, nout=1):
     if isinstance(out, tuple):
         if len(out) != nout:
@@ -67,6 +73,10 @@ class DPNPUnaryFunc(UnaryElementwiseFunc):
         self.__name__ = "DPNPUnaryFunc"
 
     def __call__(self, x, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
+        if (type(x) is dpnp_array and out is None and dtype is None and order == "K" and where is True
+                and subok is True and not kwargs):
+            # the plain call f(x): nothing to check beyond what the tensor-level object checks
+            return _wrap_new(UnaryElementwiseFunc.__call__(self, x._array_obj))
         _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
         if type(x) is _fusion.FusedValue:          # inside a function that is being fused
             if dtype is not None:
@@ -95,6 +105,17 @@ class DPNPBinaryFunc(BinaryElementwiseFunc):
         self.__name__ = "DPNPBinaryFunc"
 
     def __call__(self, x1, x2, /, out=None, *, where=True, order="K", dtype=None, subok=True, **kwargs):
+        if (out is None and dtype is None and order == "K" and where is True and subok is True
+                and not kwargs):
+            # the plain call f(x1, x2) on arrays, or an array and a Python float/int
+            t1, t2 = type(x1), type(x2)
+            if t1 is dpnp_array:
+                if t2 is dpnp_array:
+                    return _wrap_new(BinaryElementwiseFunc.__call__(self, x1._array_obj, x2._array_obj))
+                if t2 is float or t2 is int:
+                    return _wrap_new(BinaryElementwiseFunc.__call__(self, x1._array_obj, x2))
+            elif t2 is dpnp_array and (t1 is float or t1 is int):
+                return _wrap_new(BinaryElementwiseFunc.__call__(self, x1, x2._array_obj))
         if _fusion.is_traced(x1, x2):              # inside a function that is being fused
             _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
             if dtype is not None:

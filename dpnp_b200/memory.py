@@ -18,6 +18,7 @@ import threading
 
 from . import _lib
 from ._lib import check, lib
+from ._lib import native as _native
 
 __all__ = [
     "StreamQueue", "get_default_queue", "MemoryUSMDevice", "MemoryUSMShared", "MemoryUSMHost",
@@ -141,6 +142,12 @@ class MemoryUSMDevice:
         self.sycl_queue = queue if queue is not None else get_default_queue()
         self.nbytes = nbytes
         self._ptr = 0
+        self._blk = None
+        if _native is not None:
+            # the block object returns the memory to the pool when its last reference goes
+            self._blk = _native.Block(nbytes, self.sycl_queue.device, self.sycl_queue._stream)
+            self._ptr = self._blk.ptr
+            return
         self.sycl_queue.activate()
         p = C.c_void_p()
         check(lib.dpb_malloc(nbytes, C.c_void_p(self.sycl_queue.stream), C.byref(p)))
@@ -160,6 +167,11 @@ class MemoryUSMDevice:
 
     def free(self) -> None:
         ptr, self._ptr = self._ptr, 0
+        blk = getattr(self, "_blk", None)
+        if blk is not None:
+            self._blk = None
+            blk.release()
+            return
         if ptr:
             try:
                 lib.dpb_set_device(self.sycl_queue.device)
@@ -167,8 +179,10 @@ class MemoryUSMDevice:
             except Exception:  # interpreter shutdown
                 pass
 
-    def __del__(self):
-        self.free()
+    if _native is None:
+        # (with the shim, the block object inside gives the memory back by itself)
+        def __del__(self):
+            self.free()
 
     def __repr__(self):
         return f"<{type(self).__name__} {self.nbytes} bytes at 0x{self._ptr:x} on cuda:{self.sycl_queue.device}>"

@@ -21,8 +21,12 @@ from ._usmarray import usm_ndarray
 
 
 def _empty(shape, dtype, queue, order="C", usm_type="device"):
-    return usm_ndarray(shape, dtype=dtype, buffer=usm_type, order=order,
-                       buffer_ctor_kwargs={"queue": queue})
+    """Uninitialised dense array; `shape` is a validated tuple/list of extents."""
+    if type(dtype) is not np.dtype:
+        dtype = np.dtype(dtype)
+    _lib.typenum_of(dtype)
+    return usm_ndarray._new_dense(shape if type(shape) is tuple else tuple(shape), dtype, queue,
+                                  _lib.FLAG_F if order in ("F", "f") else _lib.FLAG_C, usm_type)
 
 
 def asnumpy(x) -> np.ndarray:

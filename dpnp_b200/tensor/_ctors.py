@@ -16,7 +16,7 @@ from .. import _lib
 from ..memory import normalize_queue
 from . import _tensor_impl as ti
 from ._copy_utils import _empty, astype, from_numpy
-from ._usmarray import usm_ndarray
+from ._usmarray import _normalize_shape, usm_ndarray
 
 _default_fp = np.dtype("f8")
 _default_int = np.dtype("i8")
@@ -38,6 +38,9 @@ def empty(shape, *, dtype=None, order="C", device=None, usm_type="device", sycl_
     _check_usm_type(usm_type)
     q = normalize_queue(sycl_queue, device)
     dtype = _default_fp if dtype is None else np.dtype(dtype)
+    shape = _normalize_shape(shape)
+    if len(shape) > _lib.MAX_ND:
+        raise ValueError(f"arrays with more than {_lib.MAX_ND} dimensions are not supported")
     return _empty(shape, dtype, q, order, usm_type)
 
 

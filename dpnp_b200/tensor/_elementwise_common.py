@@ -20,6 +20,7 @@ from ._manipulation_functions import _broadcast_shape_impl, broadcast_to
 from ._type_utils import (_acceptance_fn_default_binary, _acceptance_fn_default_unary,
                           _find_buf_dtype, _find_buf_dtype2, _find_buf_dtype_in_place_op,
                           _get_dtype, _get_shape, _resolve_weak_types, _validate_dtype)
+from .._lib import FLAG_C, FLAG_F
 from ._usmarray import usm_ndarray
 
 
@@ -45,6 +46,25 @@ def _scalar_to_array(value, dtype, queue):
         arr = asarray(value, dtype=dtype, sycl_queue=queue)
         _scalar_cache[key] = arr
     return arr
+
+
+_scalar_view_cache: dict = {}
+_FLOATING = frozenset(np.dtype(c) for c in ("f2", "f4", "f8"))
+
+
+def _scalar_operand(value, dtype, queue, shape):
+    """The cached 0-d array of `_scalar_to_array` broadcast to `shape` (a stride-0 view), kept per
+    (queue, type, value, shape) so that a repeated `x * 0.5` builds no Python objects at all."""
+    key = (queue._stream, dtype.char, type(value), value.hex() if type(value) is float else value, shape)
+    v = _scalar_view_cache.get(key)
+    if v is None:
+        if len(_scalar_view_cache) >= 4096:
+            _scalar_view_cache.clear()
+        v = _scalar_to_array(value, dtype, queue)
+        if shape != ():
+            v = broadcast_to(v, shape)
+        _scalar_view_cache[key] = v
+    return v
 
 
 def _coerce_usm_type(types):
@@ -80,6 +100,7 @@ class UnaryElementwiseFunc:
         self.unary_fn_ = unary_dp_impl_fn
         self.__doc__ = docs
         self.acceptance_fn_ = acceptance_fn
+        self._direct_cache = {}
 
     def __str__(self):
         return f"<{self.__name__} '{self.name_}'>"
@@ -115,9 +136,28 @@ class UnaryElementwiseFunc:
                     self.types_.append(f"{dt.char}->{r.char}")
         return self.types_
 
+    def _direct(self, dt):
+        """Result type when `dt` needs no cast buffer, else None (remembered per type)."""
+        try:
+            return self._direct_cache[dt]
+        except KeyError:
+            buf_dt, res_dt = _find_buf_dtype(dt, self.result_type_resolver_fn_, self.acceptance_fn_)
+            r = self._direct_cache[dt] = res_dt if buf_dt is None else None
+            return r
+
     def __call__(self, x, /, *, out=None, order="K"):
         if not isinstance(x, usm_ndarray):
             raise TypeError(f"Expected dpnp.tensor.usm_ndarray, got {type(x)}")
+        if out is None and order == "K":
+            # the common call: a dense input of a type the kernel takes as it is -- the general
+            # path below computes exactly this (same result type, same layout), with more steps
+            fl = x._flags
+            res_dt = self._direct(x._dtype) if fl & (FLAG_C | FLAG_F) else None
+            if res_dt is not None:
+                q = x._queue
+                out = usm_ndarray._new_dense(x._shape, res_dt, q, FLAG_C if fl & FLAG_C else FLAG_F, x._usm_type)
+                self.unary_fn_(x, out, sycl_queue=q)
+                return out
         if order not in ("C", "F", "K", "A"):
             order = "K"
         buf_dt, res_dt = _find_buf_dtype(x.dtype, self.result_type_resolver_fn_, self.acceptance_fn_)
@@ -174,6 +214,7 @@ class BinaryElementwiseFunc:
         self.__doc__ = docs
         self.acceptance_fn_ = acceptance_fn
         self.weak_type_resolver_ = weak_type_resolver
+        self._direct_cache = {}
 
     def __str__(self):
         return f"<{self.__name__} '{self.name_}'>"
@@ -249,7 +290,53 @@ class BinaryElementwiseFunc:
         return res_shape, o1_dtype, o2_dtype
 
     # ------------------------------------------------------------------- call
+    def _direct(self, dt):
+        """Result type for two operands of type `dt` when neither needs a cast buffer, else None."""
+        try:
+            return self._direct_cache[dt]
+        except KeyError:
+            b1, b2, res_dt = _find_buf_dtype2(dt, dt, self.result_type_resolver_fn_, self.acceptance_fn_)
+            r = self._direct_cache[dt] = res_dt if (b1 is None and b2 is None) else None
+            return r
+
     def __call__(self, o1, o2, /, *, out=None, order="K"):
+        if out is None and order == "K" and type(o1) is usm_ndarray and type(o2) is usm_ndarray:
+            # the common call: two arrays of one type and shape on one queue, at least one of them
+            # dense -- the general path below computes exactly this (same result type; order "K"
+            # gives C order when either input is C-contiguous, F order when both are F-contiguous)
+            f1, f2 = o1._flags, o2._flags
+            if (o1._shape == o2._shape and o1._queue is o2._queue and o1._dtype == o2._dtype
+                    and o1._usm_type == o2._usm_type):
+                order_flag = FLAG_C if (f1 | f2) & FLAG_C else (FLAG_F if f1 & f2 & FLAG_F else 0)
+                res_dt = self._direct(o1._dtype) if order_flag else None
+                if res_dt is not None:
+                    q = o1._queue
+                    out = usm_ndarray._new_dense(o1._shape, res_dt, q, order_flag, o1._usm_type)
+                    self.binary_fn_(o1, o2, out, sycl_queue=q)
+                    return out
+        elif out is None and order == "K":
+            # a dense floating array and a Python float or int: the scalar takes the array's type
+            # (NEP 50, `_promote_weak`), so this is the case above with a stride-0 second operand
+            t1, t2 = type(o1), type(o2)
+            if t1 is usm_ndarray and (t2 is float or t2 is int):
+                arr, sc, first = o1, o2, True
+            elif t2 is usm_ndarray and (t1 is float or t1 is int):
+                arr, sc, first = o2, o1, False
+            else:
+                arr = None
+            if arr is not None and arr._dtype in _FLOATING and arr._flags & (FLAG_C | FLAG_F):
+                dt = arr._dtype
+                res_dt = self._direct(dt)
+                if res_dt is not None:
+                    q = arr._queue
+                    view = _scalar_operand(sc, dt, q, arr._shape)
+                    out = usm_ndarray._new_dense(arr._shape, res_dt, q,
+                                                 FLAG_C if arr._flags & FLAG_C else FLAG_F, arr._usm_type)
+                    if first:
+                        self.binary_fn_(arr, view, out, sycl_queue=q)
+                    else:
+                        self.binary_fn_(view, arr, out, sycl_queue=q)
+                    return out
         if order not in ("K", "C", "F", "A"):
             order = "K"
         exec_q, res_usm_type = self._placement(o1, o2)

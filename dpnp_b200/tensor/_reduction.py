@@ -26,10 +26,17 @@ from ._usmarray import usm_ndarray
 
 
 def _permute_reduced_last(x, axis, int_axis_only=False):
-    nd = x.ndim
+    nd = len(x._shape)
     if axis is None:
         axis = tuple(range(nd))
         return x, axis, list(axis)
+    if type(axis) is int and -nd <= axis < nd:
+        a = axis + nd if axis < 0 else axis
+        if a == nd - 1:                     # already last: no view needed
+            return x, (a,), list(range(nd))
+        perm = [i for i in range(nd) if i != a]
+        perm.append(a)
+        return permute_dims(x, perm), (a,), perm
     if int_axis_only:
         if not isinstance(axis, (int, np.integer)):
             raise TypeError("'axis' argument expected to have type 'int' or be `None`, "
@@ -39,6 +46,8 @@ def _permute_reduced_last(x, axis, int_axis_only=False):
         axis = (axis,)
     axis = normalize_axis_tuple(axis, nd, "axis")
     perm = [i for i in range(nd) if i not in axis] + list(axis)
+    if perm == list(range(nd)):
+        return x, axis, perm
     return permute_dims(x, perm), axis, perm
 
 

@@ -18,6 +18,9 @@ def _make(name, op):
         if trailing_dims_to_accumulate != 1:
             raise ValueError("accumulation is carried out over one trailing dimension")
         _check_queue(sycl_queue, src, dst)
+        if _lib.native is not None:
+            _lib.native.accumulate(op, src._core(), dst._core(), 0, sycl_queue._stream)
+            return _events(sycl_queue)
         ds, ks = src._descriptor()
         dd, kd = dst._descriptor()
         check(lib.dpb_accumulate_over_axis(op, C.byref(ds), C.byref(dd), 0, _stream(sycl_queue)))
@@ -25,6 +28,9 @@ def _make(name, op):
 
     def include_initial(src, dst, sycl_queue, depends=()):
         _check_queue(sycl_queue, src, dst)
+        if _lib.native is not None:
+            _lib.native.accumulate(op, src._core(), dst._core(), 1, sycl_queue._stream)
+            return _events(sycl_queue)
         ds, ks = src._descriptor()
         dd, kd = dst._descriptor()
         check(lib.dpb_accumulate_over_axis(op, C.byref(ds), C.byref(dd), 1, _stream(sycl_queue)))

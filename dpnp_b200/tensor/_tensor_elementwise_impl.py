@@ -19,13 +19,26 @@ from .._lib import BINARY_OPS, UNARY_OPS, check, lib
 from ._tensor_impl import _check_queue, _events, _stream
 
 
+_nat = _lib.native
+
+
 def _make_unary(name, op):
-    def call(src, dst, sycl_queue, depends=()):
-        _check_queue(sycl_queue, src, dst)
-        ds, ks = src._descriptor()
-        dd, kd = dst._descriptor()
-        check(lib.dpb_unary_ufunc(op, C.byref(ds), C.byref(dd), _stream(sycl_queue)))
-        return _events(sycl_queue)
+    if _nat is not None:
+        nat_unary = _nat.unary
+
+        def call(src, dst, sycl_queue, depends=()):
+            dev = sycl_queue.device
+            if src._queue.device != dev or dst._queue.device != dev:
+                _check_queue(sycl_queue, src, dst)
+            nat_unary(op, src._core(), dst._core(), sycl_queue._stream)
+            return _events(sycl_queue)
+    else:
+        def call(src, dst, sycl_queue, depends=()):
+            _check_queue(sycl_queue, src, dst)
+            ds, ks = src._descriptor()
+            dd, kd = dst._descriptor()
+            check(lib.dpb_unary_ufunc(op, C.byref(ds), C.byref(dd), _stream(sycl_queue)))
+            return _events(sycl_queue)
 
     cache = {}
 
@@ -51,13 +64,23 @@ def _make_unary(name, op):
 
 
 def _make_binary(name, op):
-    def call(src1, src2, dst, sycl_queue, depends=()):
-        _check_queue(sycl_queue, src1, src2, dst)
-        d1, k1 = src1._descriptor()
-        d2, k2 = src2._descriptor()
-        dd, kd = dst._descriptor()
-        check(lib.dpb_binary_ufunc(op, C.byref(d1), C.byref(d2), C.byref(dd), _stream(sycl_queue)))
-        return _events(sycl_queue)
+    if _nat is not None:
+        nat_binary, nat_inplace = _nat.binary, _nat.binary_inplace
+
+        def call(src1, src2, dst, sycl_queue, depends=()):
+            dev = sycl_queue.device
+            if src1._queue.device != dev or src2._queue.device != dev or dst._queue.device != dev:
+                _check_queue(sycl_queue, src1, src2, dst)
+            nat_binary(op, src1._core(), src2._core(), dst._core(), sycl_queue._stream)
+            return _events(sycl_queue)
+    else:
+        def call(src1, src2, dst, sycl_queue, depends=()):
+            _check_queue(sycl_queue, src1, src2, dst)
+            d1, k1 = src1._descriptor()
+            d2, k2 = src2._descriptor()
+            dd, kd = dst._descriptor()
+            check(lib.dpb_binary_ufunc(op, C.byref(d1), C.byref(d2), C.byref(dd), _stream(sycl_queue)))
+            return _events(sycl_queue)
 
     cache = {}
 
@@ -77,12 +100,18 @@ def _make_binary(name, op):
             pass
         return res
 
-    def inplace(lhs, rhs, sycl_queue, depends=()):
-        _check_queue(sycl_queue, lhs, rhs)
-        dl, kl = lhs._descriptor()
-        dr, kr = rhs._descriptor()
-        check(lib.dpb_binary_inplace_ufunc(op, C.byref(dl), C.byref(dr), _stream(sycl_queue)))
-        return _events(sycl_queue)
+    if _nat is not None:
+        def inplace(lhs, rhs, sycl_queue, depends=()):
+            _check_queue(sycl_queue, lhs, rhs)
+            nat_inplace(op, lhs._core(), rhs._core(), sycl_queue._stream)
+            return _events(sycl_queue)
+    else:
+        def inplace(lhs, rhs, sycl_queue, depends=()):
+            _check_queue(sycl_queue, lhs, rhs)
+            dl, kl = lhs._descriptor()
+            dr, kr = rhs._descriptor()
+            check(lib.dpb_binary_inplace_ufunc(op, C.byref(dl), C.byref(dr), _stream(sycl_queue)))
+            return _events(sycl_queue)
 
     call.__name__ = f"_{name}"
     result_type.__name__ = f"_{name}_result_type"
@@ -104,6 +133,9 @@ for _n, _op in BINARY_OPS.items():
 
 def _divide_by_scalar(src, scalar, dst, sycl_queue, depends=()):
     _check_queue(sycl_queue, src, dst)
+    if _nat is not None:
+        _nat.divide_by_scalar(src._core(), float(scalar), dst._core(), sycl_queue._stream)
+        return _events(sycl_queue)
     ds, ks = src._descriptor()
     dd, kd = dst._descriptor()
     check(lib.dpb_divide_by_scalar(C.byref(ds), float(scalar), C.byref(dd), _stream(sycl_queue)))

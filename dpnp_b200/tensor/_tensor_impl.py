@@ -47,8 +47,14 @@ def _check_queue(q, *arrays):
             raise ValueError("Execution queue is not compatible with allocation queues")
 
 
+_nat = _lib.native
+
+
 def _where(condition, x1, x2, dst, sycl_queue, depends=()):
     _check_queue(sycl_queue, condition, x1, x2, dst)
+    if _nat is not None:
+        _nat.where(condition._core(), x1._core(), x2._core(), dst._core(), sycl_queue._stream)
+        return _events(sycl_queue)
     dc, kc = condition._descriptor()
     d1, k1 = x1._descriptor()
     d2, k2 = x2._descriptor()
@@ -59,6 +65,9 @@ def _where(condition, x1, x2, dst, sycl_queue, depends=()):
 
 def _copy_usm_ndarray_into_usm_ndarray(src, dst, sycl_queue, depends=()):
     _check_queue(sycl_queue, src, dst)
+    if _nat is not None:
+        _nat.copy(src._core(), dst._core(), sycl_queue._stream)
+        return _events(sycl_queue)
     ds, ks = src._descriptor()
     dd, kd = dst._descriptor()
     check(lib.dpb_copy_array_into_array(C.byref(ds), C.byref(dd), _stream(sycl_queue)))

@@ -14,21 +14,38 @@ from .._lib import REDUCE_OPS, SEARCH_OPS, check, lib
 from ._tensor_impl import _check_queue, _events, _stream
 
 
+_nat = _lib.native
+
+
 def _make_reduce(name, op):
     def call(src, trailing_dims_to_reduce, dst, sycl_queue, depends=()):
         _check_queue(sycl_queue, src, dst)
+        if _nat is not None:
+            _nat.reduce(op, src._core(), int(trailing_dims_to_reduce), dst._core(), sycl_queue._stream)
+            return _events(sycl_queue)
         ds, ks = src._descriptor()
         dd, kd = dst._descriptor()
         check(lib.dpb_reduction_over_axis(op, C.byref(ds), int(trailing_dims_to_reduce), C.byref(dd),
                                           _stream(sycl_queue)))
         return _events(sycl_queue)
 
+    cache = {}
+
     def supported(arg_dtype, out_dtype, dst_usm_type=None, sycl_queue=None):
         try:
-            return bool(lib.dpb_reduce_dtype_supported(op, _lib.typenum_of(arg_dtype),
-                                                       _lib.typenum_of(out_dtype)))
+            return cache[(arg_dtype, out_dtype)]
+        except (KeyError, TypeError):
+            pass
+        try:
+            ok = bool(lib.dpb_reduce_dtype_supported(op, _lib.typenum_of(arg_dtype),
+                                                     _lib.typenum_of(out_dtype)))
         except TypeError:
             return False
+        try:
+            cache[(arg_dtype, out_dtype)] = ok
+        except TypeError:
+            pass
+        return ok
 
     call.__name__ = f"_{name}_over_axis"
     supported.__name__ = f"_{name}_over_axis_dtype_supported"
@@ -38,6 +55,9 @@ def _make_reduce(name, op):
 def _make_search(name, op):
     def call(src, trailing_dims_to_reduce, dst, sycl_queue, depends=()):
         _check_queue(sycl_queue, src, dst)
+        if _nat is not None:
+            _nat.search(op, src._core(), int(trailing_dims_to_reduce), dst._core(), sycl_queue._stream)
+            return _events(sycl_queue)
         ds, ks = src._descriptor()
         dd, kd = dst._descriptor()
         check(lib.dpb_search_over_axis(op, C.byref(ds), int(trailing_dims_to_reduce), C.byref(dd),

@@ -16,7 +16,8 @@ import operator
 import numpy as np
 
 from .. import _lib
-from .._lib import FLAG_C, FLAG_F, FLAG_W, check, dpb_array, lib
+from .._lib import _TYPENUM, FLAG_C, FLAG_F, FLAG_W, check, dpb_array, lib
+from .._lib import native as _native
 from ..memory import MemoryUSMDevice, StreamQueue, get_default_queue, normalize_queue
 
 
@@ -125,6 +126,12 @@ class usm_ndarray:
     """N-dimensional strided array over CUDA device memory."""
 
     __array_priority__ = 100.0
+    # per-object caches, filled on first use (class-level defaults keep construction cheap)
+    _desc_cache = None
+    _core_cache = None
+    _extent_cache = 0
+    _array_namespace = None
+    _usm_type = "device"
 
     def __init__(self, shape, dtype=None, strides=None, buffer="device", offset=0, order="C",
                  buffer_ctor_kwargs=None, array_namespace=None):
@@ -188,7 +195,8 @@ class usm_ndarray:
         self._dtype = dtype
         self._flags = _contig_flags(shape, strides) | FLAG_W
         self._queue = mem.sycl_queue
-        self._array_namespace = array_namespace
+        if array_namespace is not None:
+            self._array_namespace = array_namespace
 
     # ------------------------------------------------------------ internals
     @classmethod
@@ -202,9 +210,46 @@ class usm_ndarray:
         self._dtype = dtype
         self._flags = _contig_flags(self._shape, self._strides) | (FLAG_W if writable else 0)
         self._queue = queue
-        self._usm_type = usm_type
-        self._array_namespace = None
+        if usm_type != "device":
+            self._usm_type = usm_type
         return self
+
+    @classmethod
+    def _new_dense(cls, shape, dtype, queue, order_flag=FLAG_C, usm_type="device"):
+        """New array of `shape` (a tuple of non-negative ints) in C (FLAG_C) or F (FLAG_F) order
+        on `queue`: what ``usm_ndarray(shape, dtype, buffer=usm_type, order=...)`` builds, minus
+        the argument checks -- the allocation of every elementwise and reduction result."""
+        self = cls.__new__(cls)
+        n = 1
+        for d in shape:
+            n *= d
+        self._base = mem = MemoryUSMDevice((n if n > 0 else 1) * dtype.itemsize, queue)
+        self._ptr = mem._ptr
+        self._shape = shape
+        if len(shape) == 1:
+            self._strides = (1,)
+            self._flags = FLAG_C | FLAG_F | FLAG_W
+        else:
+            self._strides = _dense_strides(shape, "C" if order_flag == FLAG_C else "F")
+            # a dense array is contiguous both ways when at most one extent exceeds 1
+            big = 0
+            for d in shape:
+                if d > 1:
+                    big += 1
+            self._flags = ((FLAG_C | FLAG_F) if (n == 0 or big <= 1) else order_flag) | FLAG_W
+        self._dtype = dtype
+        self._queue = queue
+        if usm_type != "device":
+            self._usm_type = usm_type
+        return self
+
+    def _core(self):
+        """The array's view for the pybind11 shim (built once per array object)."""
+        c = self._core_cache
+        if c is None:
+            c = self._core_cache = _native.ArrayCore(self._ptr, _TYPENUM[self._dtype], self._flags,
+                                                     self._queue.device, self._shape, self._strides)
+        return c
 
     def _like(self, ptr, shape, strides):
         return usm_ndarray._view(self._base, ptr, shape, strides, self._dtype, self._queue,
@@ -212,7 +257,7 @@ class usm_ndarray:
 
     def _descriptor(self):
         """(dpb_array, keepalive) for the C ABI; built once per array object."""
-        cached = getattr(self, "_desc_cache", None)
+        cached = self._desc_cache
         if cached is not None:
             return cached
         nd = len(self._shape)
@@ -231,7 +276,7 @@ class usm_ndarray:
 
     def _byte_extent(self):
         """Half-open range of byte addresses the array can touch (None when empty)."""
-        ext = getattr(self, "_extent_cache", 0)
+        ext = self._extent_cache
         if ext != 0:
             return ext
         lo = hi = 0
@@ -262,6 +307,7 @@ class usm_ndarray:
         r = reshape(self, new_shape, copy=False)
         self._shape, self._strides, self._flags = r._shape, r._strides, r._flags
         self._desc_cache = None
+        self._core_cache = None
         self._extent_cache = 0
 
     @property

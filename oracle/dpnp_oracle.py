@@ -196,22 +196,77 @@ def sum_int(x, axis=None, dtype=None):
     return np.sum(x, axis=axis, dtype=dt)
 
 
-def max_(x, axis=None):
+def max_(x, axis=None, keepdims=False):
     """NaN-propagating maximum (include/utils/sycl_utils.hpp:332-352) == np.max."""
-    return np.max(x, axis=axis)
+    if np.asarray(x).dtype.kind == "c":
+        return complex_extreme(x, axis, True, keepdims)[0]
+    return np.max(x, axis=axis, keepdims=keepdims)
 
 
-def min_(x, axis=None):
-    return np.min(x, axis=axis)
+def min_(x, axis=None, keepdims=False):
+    if np.asarray(x).dtype.kind == "c":
+        return complex_extreme(x, axis, False, keepdims)[0]
+    return np.min(x, axis=axis, keepdims=keepdims)
+
+
+def _has_nan(z):
+    return z.real != z.real or z.imag != z.imag
+
+
+def _complex_better(val, best, want_max):
+    """greater_complex / less_complex of include/utils/math_utils.hpp:43-69: real parts decide
+    unless equal, then imaginary parts; any comparison against a NaN part is false."""
+    if val.real == best.real:
+        return val.imag > best.imag if want_max else val.imag < best.imag
+    if val.imag != val.imag or best.imag != best.imag:
+        return False
+    return val.real > best.real if want_max else val.real < best.real
+
+
+def complex_extreme(x, axis=None, want_max=True, keepdims=False):
+    """(values, positions) of max/min of a complex array, folding each reduced lane from the
+    left with the reference's rules: max_complex / min_complex keep the running value when
+    it holds a NaN or wins the comparison, else take the new one
+    (include/utils/math_utils.hpp:100-131); the search kernels replace the running value when
+    the new one wins or holds a NaN and the running one does not -- a lane's first NaN stays
+    (include/kernels/reductions.hpp:1914-1963 with the first-occurrence tie rule of
+    :2062-2117).  Pure-Python loops: for small arrays."""
+    x = np.asarray(x)
+    if axis is None:
+        lanes = x.reshape(1, -1)
+        out_shape = (1,) * x.ndim if keepdims else ()
+    else:
+        axes = tuple(sorted(a % x.ndim for a in (axis if isinstance(axis, (tuple, list)) else (axis,))))
+        rest = [i for i in range(x.ndim) if i not in axes]
+        moved = np.transpose(x, rest + list(axes))
+        kept = moved.shape[:len(rest)]
+        lanes = np.ascontiguousarray(moved).reshape(int(np.prod(kept, dtype=np.int64)), -1)
+        out_shape = tuple(1 if i in axes else x.shape[i] for i in range(x.ndim)) if keepdims else kept
+    vals = np.empty(lanes.shape[0], dtype=x.dtype)
+    pos = np.empty(lanes.shape[0], dtype=np.int64)
+    for r in range(lanes.shape[0]):
+        best, at = lanes[r, 0], 0
+        for m in range(1, lanes.shape[1]):
+            v = lanes[r, m]
+            if _has_nan(best):
+                break
+            if _has_nan(v) or _complex_better(v, best, want_max):
+                best, at = v, m
+        vals[r], pos[r] = best, at
+    return vals.reshape(out_shape), pos.reshape(out_shape)
 
 
 def argmax(x, axis=None):
     """First occurrence of the maximum, NaN is the maximum
     (include/kernels/reductions.hpp:1933-1963,2062-2117) == np.argmax."""
+    if np.asarray(x).dtype.kind == "c":
+        return complex_extreme(x, axis, True)[1]
     return np.argmax(x, axis=axis)
 
 
 def argmin(x, axis=None):
+    if np.asarray(x).dtype.kind == "c":
+        return complex_extreme(x, axis, False)[1]
     return np.argmin(x, axis=axis)
 
 

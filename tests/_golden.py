@@ -13,10 +13,11 @@ def load_cases():
         cases = json.load(fh)
     data = np.load(os.path.join(_DIR, "known_answers.npz"))
     for c in cases:
-        c["x"] = data[f"{c['name']}__x"]
+        c["x"] = data[f"{c.get('x_from', c['name'])}__x"]
         c["expected"] = data[f"{c['name']}__expected"]
-        ykey = f"{c['name']}__y"
-        c["y"] = data[ykey] if ykey in data.files else None
+        for key in ("y", "cond"):
+            k = f"{c['name']}__{key}"
+            c[key] = data[k] if k in data.files else None
     return cases
 
 
@@ -24,7 +25,7 @@ def apply_view(x, steps, xp):
     """Apply the view steps of a case to a NumPy array (xp=np) or a device array."""
     for kind, arg in steps:
         if kind == "flip":
-            x = xp.flip(x, axis=arg)
+            x = xp.flip(x, axis=arg) if arg is not None else xp.flip(x)
         elif kind == "permute":
             x = xp.transpose(x, arg) if xp is np else x.transpose(*arg)
         elif kind == "slice":

@@ -12,6 +12,7 @@ Run from the repository root:  python tests/golden/make_golden.py
 
 from __future__ import annotations
 
+import hashlib
 import json
 import os
 
@@ -20,15 +21,22 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 arrays: dict[str, np.ndarray] = {}
 cases: list[dict] = []
+_stored_inputs: dict[tuple, str] = {}
 
 
 def case(name, source, op, x, expected, *, view=None, exact=True, **params):
     """Register one case.  `view` = list of ("flip", axis) / ("slice", spec) /
     ("permute", axes) / ("reshape", shape) steps applied to the stored input before the op."""
-    arrays[f"{name}__x"] = np.ascontiguousarray(x)
+    x = np.ascontiguousarray(x)
+    digest = (x.dtype.str, x.shape, hashlib.sha1(x.tobytes()).hexdigest())
+    entry = {"name": name, "source": source, "op": op, "view": view or [], "exact": exact, "params": params}
+    if x.nbytes >= 256 and digest in _stored_inputs:
+        entry["x_from"] = _stored_inputs[digest]     # the same input as an earlier case: stored once
+    else:
+        arrays[f"{name}__x"] = x
+        _stored_inputs[digest] = name
     arrays[f"{name}__expected"] = np.asarray(expected)
-    cases.append({"name": name, "source": source, "op": op, "view": view or [], "exact": exact,
-                  "params": params})
+    cases.append(entry)
 
 
 T_SUM = "dpnp/tests/tensor/test_tensor_sum.py"
@@ -182,6 +190,120 @@ for dt in ("f4", "f8"):
          np.array([np.nan, np.inf, 0.0, 1.0, 1.0], dtype=dt))
 case("erf_nan_inf", f"{T_SPECIAL}:38-46", "erf", np.array([np.nan, -np.inf, np.inf]), np.array([np.nan, -1.0, 1.0]))
 case("erf_zeros_signbit", f"{T_SPECIAL}:48-57", "erf", np.array([0.0, -0.0]), np.array([0.0, -0.0]))
+
+# ---- where -----------------------------------------------------------------------------
+T_WHERE = "dpnp/tests/tensor/test_usm_ndarray_search_functions.py"
+
+
+def where_case(name, source, cond, x1, x2, expected, *, views=None, exact=True):
+    """`views` maps "cond"/"x"/"y" to view steps applied to the stored operand before the call."""
+    arrays[f"{name}__cond"] = np.ascontiguousarray(cond)
+    arrays[f"{name}__y"] = np.ascontiguousarray(x2)
+    case(name, source, "where", x1, expected, exact=exact, views=views or {})
+
+
+cond = np.array([[True, False, False], [False, True, False], [False, False, True],
+                 [False, False, False], [True, True, True]])
+eye_like = np.array([[1, 0, 0], [0, 1, 0], [0, 0, 1], [0, 0, 0], [1, 1, 1]])
+where_case("where_basic_0d_operands", f"{T_WHERE}:69-86", cond, np.asarray(1), np.asarray(0), eye_like)
+where_case("where_basic_full_operands", f"{T_WHERE}:88-89", cond, np.ones(cond.shape), np.zeros(cond.shape),
+           eye_like.astype("f8"))
+where_case("where_basic_column_operands", f"{T_WHERE}:91-96", cond, np.ones((5, 1), dtype="i4"),
+           np.zeros((5, 1), dtype="i4"), eye_like.astype("i4"))
+c4 = np.array([True, False, True, False])
+a4 = np.array([np.nan, 2.0, np.inf, 3.0], dtype="f4")
+b4 = np.array([2.0, np.nan, 3.0, np.inf], dtype="f4")
+# expected values written out element by element: cond ? x1 : x2
+where_case("where_nan_inf", f"{T_WHERE}:189-203", c4, a4, b4, np.array([np.nan, np.nan, np.inf, np.inf], dtype="f4"))
+# a floating condition: NaN and inf are non-zero, hence true; bool and float32 promote to float32
+where_case("where_float_condition", f"{T_WHERE}:205-207", a4, c4, b4, np.array([1.0, 0.0, 1.0, 0.0], dtype="f4"))
+s0, s1 = 4, 9
+cond_full = np.array([True, False, False, False, True, True, False, True, False] * s0).reshape(s0, s1)
+x1_full = np.arange(s0 * 3 * 2, dtype="i4").reshape(s0, 6)
+x2_full = np.arange(s0 * 3 * 3, dtype="i4").reshape(s0, 9)
+cv, xv, yv = cond_full[:, ::3], x1_full[:, ::2], x2_full[:, ::3]
+sl3, sl2 = [[None, None, None], [None, None, 3]], [[None, None, None], [None, None, 2]]
+
+
+def pick(c_, a_, b_):
+    out = np.empty(c_.shape, dtype=a_.dtype)
+    for idx in np.ndindex(*c_.shape):
+        out[idx] = a_[idx] if c_[idx] else b_[idx]
+    return out
+
+
+where_case("where_strided", f"{T_WHERE}:294-313", cond_full, x1_full, x2_full, pick(cv, xv, yv),
+           views={"cond": [["slice", sl3]], "x": [["slice", sl2]], "y": [["slice", sl3]]})
+where_case("where_strided_flipped_x1", f"{T_WHERE}:315-320", cond_full, x1_full, x2_full,
+           pick(cv, xv[::-1, ::-1], yv),
+           views={"cond": [["slice", sl3]], "x": [["slice", sl2], ["flip", None]], "y": [["slice", sl3]]})
+where_case("where_strided_flipped_cond", f"{T_WHERE}:322-326", cond_full, x1_full, x2_full,
+           pick(cv[::-1, ::-1], xv, yv),
+           views={"cond": [["slice", sl3], ["flip", None]], "x": [["slice", sl2]], "y": [["slice", sl3]]})
+where_case("where_unaligned", f"{T_WHERE}:451-461", np.ones(513, dtype="i4"), np.full(512, 2, dtype="i4"),
+           np.zeros(512, dtype="i4"), np.full(512, 2, dtype="i4"), views={"cond": [["slice", [[1, None, None]]]]})
+
+# ---- the ported CuPy reduction suite: max/min/argmax/argmin against NumPy ------------------
+# Its inputs come from testing.shaped_random (RandomState(0).rand(*shape) * 10 cast to the type;
+# booleans from randint(2); complex from two draws) in C and F order, and its expected value is
+# NumPy's result on the same input (testing.numpy_cupy_allclose), which is what is stored here.
+T_CUPY = "dpnp/tests/third_party/cupy/core_tests/test_ndarray_reduction.py"
+
+
+def shaped_random(shape, dtype, scale=10, seed=0):
+    rng = np.random.RandomState(seed)
+    dtype = np.dtype(dtype)
+    if dtype == "?":
+        a = rng.randint(2, size=shape)
+    elif dtype.kind == "c":
+        a = rng.rand(*shape) + 1j * rng.rand(*shape)
+        a *= scale
+    else:
+        a = rng.rand(*shape) * scale
+    return np.asarray(a, dtype=dtype)
+
+
+ALL_DTYPES = ("?", "i1", "u1", "i2", "u2", "i4", "u4", "i8", "u8", "f2", "f4", "f8", "c8", "c16")
+CUPY_SHAPES = [  # (tag, lines for max / min / argmax / argmin, shape, axis, keepdims)
+    ("all", (45, 119, 193, 249), (2, 3), None, False),
+    ("all_keepdims", (51, 125, None, None), (2, 3), None, True),
+    ("axis_large", (57, 131, 199, 255), (3, 1000), 0, False),
+    ("axis0", (63, 137, 205, 261), (2, 3, 4), 0, False),
+    ("axis1", (69, 143, 211, 267), (2, 3, 4), 1, False),
+    ("axis2", (75, 149, 217, 273), (2, 3, 4), 2, False),
+    ("multiple_axes", (81, 155, None, None), (2, 3, 4), [1, 2], False),
+    ("multiple_axes_keepdims", (87, 161, None, None), (2, 3, 4), [1, 2], True),
+]
+for fn_i, fn in enumerate(("max", "min", "argmax", "argmin")):
+    for tag, lines, shape, axis, keepdims in CUPY_SHAPES:
+        if lines[fn_i] is None:
+            continue
+        for dt in ALL_DTYPES:
+            a = shaped_random(shape, dt)
+            ax = tuple(axis) if isinstance(axis, list) else axis
+            kw = {"keepdims": True} if keepdims else {}
+            want = getattr(np, fn)(a, axis=ax, **kw)
+            for order in ("C", "F"):
+                case(f"cupy_{fn}_{tag}_{np.dtype(dt).name}_{order}", f"{T_CUPY}:{lines[fn_i]}-{lines[fn_i] + 4}",
+                     fn, a, want, axis=axis, order=order, **kw)
+    first = {"max": 93, "min": 167, "argmax": 223, "argmin": 279}[fn]
+    for order in ("C", "F"):
+        for dt in ("f2", "f4", "f8"):
+            a = np.array([float("nan"), 1, -1], dt)
+            case(f"cupy_{fn}_nan_{np.dtype(dt).name}_{order}", f"{T_CUPY}:{first}-{first + 4}", fn, a,
+                 getattr(np, fn)(a), axis=None, order=order)
+            if fn in ("max", "min"):
+                inf = -float("inf") if fn == "max" else float("inf")
+                a = np.array([inf, inf], dt)
+                case(f"cupy_{fn}_inf_{np.dtype(dt).name}_{order}", f"{T_CUPY}:{first + 18}-{first + 23}", fn, a,
+                     getattr(np, fn)(a), axis=None, order=order)
+        for dt in ("c8", "c16"):
+            a = np.array([float("nan"), 1, -1], dt)
+            case(f"cupy_{fn}_nan_real_{np.dtype(dt).name}_{order}", f"{T_CUPY}:{first + 6}-{first + 10}", fn, a,
+                 getattr(np, fn)(a), axis=None, order=order)
+            a = np.array([float("nan") * 1.0j, 1.0j, -1.0j], dt)
+            case(f"cupy_{fn}_nan_imag_{np.dtype(dt).name}_{order}", f"{T_CUPY}:{first + 12}-{first + 16}", fn, a,
+                 getattr(np, fn)(a), axis=None, order=order)
 
 np.savez_compressed(os.path.join(HERE, "known_answers.npz"), **arrays)
 with open(os.path.join(HERE, "known_answers.json"), "w") as fh:

@@ -18,8 +18,15 @@ def device_eval(c):
     op, ax = c["op"], axis_of(c["params"])
     if op == "sum":
         return dp.sum(x, axis=ax, dtype=c["params"].get("dtype"))
-    if op in ("max", "min", "argmax", "argmin", "mean"):
+    if op in ("max", "min"):
+        return getattr(dp, op)(x, axis=ax, keepdims=c["params"].get("keepdims", False))
+    if op in ("argmax", "argmin", "mean"):
         return getattr(dp, op)(x, axis=ax)
+    if op == "where":
+        views = c["params"]["views"]
+        return dp.where(apply_view(dp.asarray(c["cond"]), views.get("cond", []), dp),
+                        apply_view(x, views.get("x", []), dp),
+                        apply_view(dp.asarray(c["y"]), views.get("y", []), dp))
     if op == "add":
         return dp.add(x, dp.asarray(c["y"]))
     if op in ("exp", "erf"):

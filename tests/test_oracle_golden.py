@@ -24,9 +24,14 @@ def oracle_eval(c):
             return np.asarray(s).astype(dt)
         return np.asarray(orc.sum_int(x, axis=ax, dtype=dt))
     if op == "max":
-        return np.asarray(orc.max_(x, axis=ax))
+        return np.asarray(orc.max_(x, axis=ax, keepdims=c["params"].get("keepdims", False)))
     if op == "min":
-        return np.asarray(orc.min_(x, axis=ax))
+        return np.asarray(orc.min_(x, axis=ax, keepdims=c["params"].get("keepdims", False)))
+    if op == "where":
+        views = c["params"]["views"]
+        return np.asarray(orc.where(apply_view(c["cond"], views.get("cond", []), np),
+                                    apply_view(x, views.get("x", []), np),
+                                    apply_view(c["y"], views.get("y", []), np)))
     if op == "argmax":
         return np.asarray(orc.argmax(x, axis=ax))
     if op == "argmin":
