@@ -12,7 +12,7 @@ argmax, argmin, plus ``fuse`` (a chain of elementwise calls as one launch).  All
 import numpy as _np
 
 from . import _lib, memory, random, scipy, tensor
-from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, argmax, argmin, array, asarray,
+from ._iface import (all, amax, amin, any, arange, are_same_logical_tensors, argmax, argmin, array, asarray, ascontiguousarray,
                      asnumpy, astype, broadcast_to, check_limitations, copy, copyto, count_nonzero,
                      cumlogsumexp, cumprod, cumsum, cumulative_prod, cumulative_sum,
                      default_float_type, empty, empty_like, expand_dims, flip, from_dlpack, full, full_like,
@@ -34,6 +34,7 @@ from ._ufuncs import (acos, acosh, angle, arccos, arccosh, arcsin, arcsinh, arct
 from .dpnp_array import dpnp_array
 from .dpnp_array import dpnp_array as ndarray
 from .memory import ExecutionPlacementError, StreamQueue, get_default_queue
+from . import sharded
 
 __version__ = "0.1.0"
 

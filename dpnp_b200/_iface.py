@@ -146,6 +146,18 @@ def asarray(a, dtype=None, order=None, *, device=None, usm_type=None, sycl_queue
                              sycl_queue=sycl_queue, copy=copy))
 
 
+def ascontiguousarray(a, dtype=None, *, like=None, device=None, usm_type=None, sycl_queue=None):
+    """C-contiguous array with the contents of `a`; `a` itself when it already is one
+    (dpnp/dpnp_iface_arraycreation.py: ascontiguousarray)."""
+    if like is not None:
+        raise NotImplementedError("like keyword is not supported")
+    if isinstance(a, (dpnp_array, usm_ndarray)):
+        u = get_usm_ndarray(a)
+        if u.flags.c_contiguous and (dtype is None or np.dtype(dtype) == u.dtype):
+            return _wrap(u)
+    return asarray(a, dtype=dtype, order="C", device=device, usm_type=usm_type, sycl_queue=sycl_queue)
+
+
 def array(a, dtype=None, *, copy=True, order="K", subok=False, ndmin=0, like=None, device=None,
           usm_type=None, sycl_queue=None):
     if subok or like is not None:
@@ -220,8 +232,16 @@ def _reduction_res_dt(a, dtype):
     return _default_accumulation_dtype(a.dtype) if dtype is None else np.dtype(dtype)
 
 
+def _sharded(a):
+    """The hook of a sharded array (dpnp_b200.sharded.ShardedArray), else None."""
+    return None if type(a) is dpnp_array else getattr(a, "__dpnp_sharded__", None)
+
+
 def sum(a, axis=None, dtype=None, out=None, keepdims=False, initial=None, where=True):
     check_limitations(initial=initial, where=where)
+    sh = _sharded(a)
+    if sh is not None:
+        return sh("sum", axis, dtype, keepdims, out)
     usm_a = get_usm_ndarray(a)
     return _wrap_reduction_call(usm_a, out, dpt.sum, _reduction_res_dt(usm_a, dtype), axis=axis,
                                 dtype=dtype, keepdims=keepdims)
@@ -236,12 +256,18 @@ def prod(a, axis=None, dtype=None, out=None, keepdims=False, initial=None, where
 
 def max(a, axis=None, out=None, keepdims=False, initial=None, where=True):
     check_limitations(initial=initial, where=where)
+    sh = _sharded(a)
+    if sh is not None:
+        return sh("max", axis, None, keepdims, out)
     usm_a = get_usm_ndarray(a)
     return _wrap_reduction_call(usm_a, out, dpt.max, usm_a.dtype, axis=axis, keepdims=keepdims)
 
 
 def min(a, axis=None, out=None, keepdims=False, initial=None, where=True):
     check_limitations(initial=initial, where=where)
+    sh = _sharded(a)
+    if sh is not None:
+        return sh("min", axis, None, keepdims, out)
     usm_a = get_usm_ndarray(a)
     return _wrap_reduction_call(usm_a, out, dpt.min, usm_a.dtype, axis=axis, keepdims=keepdims)
 
@@ -250,17 +276,32 @@ amax, amin = max, min
 
 
 def argmax(a, axis=None, out=None, *, keepdims=False):
+    sh = _sharded(a)
+    if sh is not None:
+        if out is not None:
+            raise NotImplementedError("out= is not supported for reductions of sharded arrays")
+        return sh("argmax", axis, keepdims)
     usm_a = get_usm_ndarray(a)
     return _wrap_reduction_call(usm_a, out, dpt.argmax, np.dtype("i8"), axis=axis, keepdims=keepdims)
 
 
 def argmin(a, axis=None, out=None, *, keepdims=False):
+    sh = _sharded(a)
+    if sh is not None:
+        if out is not None:
+            raise NotImplementedError("out= is not supported for reductions of sharded arrays")
+        return sh("argmin", axis, keepdims)
     usm_a = get_usm_ndarray(a)
     return _wrap_reduction_call(usm_a, out, dpt.argmin, np.dtype("i8"), axis=axis, keepdims=keepdims)
 
 
 def mean(a, /, axis=None, dtype=None, out=None, keepdims=False, *, where=True):
     check_limitations(where=where)
+    sh = _sharded(a)
+    if sh is not None:
+        if out is not None or dtype is not None:
+            raise NotImplementedError("out= and dtype= are not supported for the mean of a sharded array")
+        return sh("mean", axis, keepdims)
     res = dpt.mean(get_usm_ndarray(a), axis=axis, keepdims=keepdims)
     if dtype is not None:
         res = dpt.astype(res, dtype)

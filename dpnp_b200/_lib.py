@@ -163,6 +163,16 @@ PROTOTYPES = {
     "dpb_linspace_step": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
     "dpb_linspace_affine": (_i, [_i, _vp, _i64, _vp, _vp, _i, _vp]),
     "dpb_take_one": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
+    "dpb_comm_load": (_i, [C.c_char_p]),
+    "dpb_comm_nccl_version": (_i, [C.POINTER(_i)]),
+    "dpb_comm_unique_id": (_i, [_vp]),
+    "dpb_comm_init": (_i, [_i, _i, _vp, _pvp]),
+    "dpb_comm_destroy": (_i, [_vp]),
+    "dpb_comm_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "dpb_comm_allgather": (_i, [_vp, _vp, _vp, _i64, _vp]),
+    "dpb_comm_sum_ordered": (_i, [_vp, _i, _vp, _vp, _i64, _vp]),
+    "dpb_comm_extreme": (_i, [_vp, _i, _i, _vp, _vp, _i64, _vp]),
+    "dpb_comm_arg_extreme": (_i, [_vp, _i, _i, _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
     "dpb_last_kernel": (C.c_char_p, []),
     "dpb_launch_count": (_i64, []),
     "dpb_reset_launch_count": (None, []),

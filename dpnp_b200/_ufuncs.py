@@ -15,6 +15,8 @@ import numpy as np
 from . import _fusion
 from . import tensor as dpt
 from .dpnp_array import dpnp_array
+from .sharded import ShardedArray
+from .sharded import elementwise as _sharded_elementwise
 from .tensor import _elementwise_funcs as ef
 from .tensor._elementwise_common import BinaryElementwiseFunc, UnaryElementwiseFunc
 from .tensor._usmarray import usm_ndarray
@@ -77,6 +79,10 @@ class DPNPUnaryFunc(UnaryElementwiseFunc):
                 and subok is True and not kwargs):
             # the plain call f(x): nothing to check beyond what the tensor-level object checks
             return _wrap_new(UnaryElementwiseFunc.__call__(self, x._array_obj))
+        if type(x) is ShardedArray:                # slab-wise on every rank, no communication
+            _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+            kw = {k: v for k, v in (("out", out), ("dtype", dtype)) if v is not None}
+            return _sharded_elementwise(self._public_name, x, order=order, **kw)
         _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
         if type(x) is _fusion.FusedValue:          # inside a function that is being fused
             if dtype is not None:
@@ -116,6 +122,10 @@ class DPNPBinaryFunc(BinaryElementwiseFunc):
                     return _wrap_new(BinaryElementwiseFunc.__call__(self, x1._array_obj, x2))
             elif t2 is dpnp_array and (t1 is float or t1 is int):
                 return _wrap_new(BinaryElementwiseFunc.__call__(self, x1, x2._array_obj))
+        if type(x1) is ShardedArray or type(x2) is ShardedArray:
+            _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+            kw = {k: v for k, v in (("out", out), ("dtype", dtype)) if v is not None}
+            return _sharded_elementwise(self._public_name, x1, x2, order=order, **kw)
         if _fusion.is_traced(x1, x2):              # inside a function that is being fused
             _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
             if dtype is not None:
@@ -259,3 +269,10 @@ class DPNPRound(DPNPUnaryFunc):
 
 
 round = around = DPNPRound(ef.round, "round")
+
+
+# name under which each ufunc object is reachable in the package (and in NumPy): sharded arrays
+# apply the function of that name to their local parts
+for _n, _o in list(globals().items()):
+    if isinstance(_o, (DPNPUnaryFunc, DPNPBinaryFunc)) and not hasattr(_o, "_public_name"):
+        _o._public_name = _n

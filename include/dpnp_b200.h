@@ -582,6 +582,46 @@ int dpb_linspace_affine(int typenum, void *dst, int64_t nelems, const void *star
  * (dpnp/tensor/_usmarray.pyx: __getitem__, _copy_utils.py:_copy_to_numpy). */
 int dpb_take_one(int typenum, const void *src, int64_t nelems, const void *index, void *dst, void *stream);
 
+/* ------------------------------------------- multi-GPU: combining partials */
+/* One process per GPU; arrays are sharded along their leading axis.  The reference has no
+ * multi-device execution -- an array and every operation on it are tied to one queue
+ * (dpnp/tensor/_compute_follows_data.pyx:67-160, dpnp/tensor/_usmarray.pyx:1113-1191) -- so
+ * these entry points replace nothing; they are what a sharded reduction needs after each GPU
+ * has reduced its own shard with dpb_reduction_over_axis / dpb_search_over_axis.  NCCL is
+ * loaded at run time (dlopen); every call is enqueued on `stream`; no kernel of this library
+ * waits on another GPU. */
+
+/* Load NCCL from `libnccl_path` (NULL or "": the loader's default libnccl.so.2). */
+int dpb_comm_load(const char *libnccl_path);
+/* Version code of the loaded NCCL (ncclGetVersion). */
+int dpb_comm_nccl_version(int *version);
+/* 128-byte id created by rank 0 (ncclGetUniqueId); the caller hands it to the other ranks. */
+int dpb_comm_unique_id(void *id128);
+/* Communicator of `world` ranks on the current device (ncclCommInitRank); world == 1 needs
+ * neither NCCL nor an id.  Errors: rank outside the group, missing id, NCCL failures. */
+int dpb_comm_init(int rank, int world, const void *id128, void **comm);
+int dpb_comm_destroy(void *comm);
+int dpb_comm_info(void *comm, int *rank, int *world);
+/* recv[r * nbytes ...] = rank r's send buffer (device memory, nbytes per rank). */
+int dpb_comm_allgather(void *comm, const void *send, void *recv, int64_t nbytes, void *stream);
+/* out[i] = partial_0[i] + partial_1[i] + ... in rank order, identical bits on every rank:
+ * all-gather into the communicator's gather buffer, then one kernel. */
+int dpb_comm_sum_ordered(void *comm, int typenum, const void *partial, void *out, int64_t count,
+                         void *stream);
+/* out[i] = max / min over ranks of partial_r[i], NaN propagating as in the reductions. */
+int dpb_comm_extreme(void *comm, int typenum, int is_max, const void *partial, void *out,
+                     int64_t count, void *stream);
+/* Global argmax / argmin of a flattened sharded array.  `src` is this rank's shard (`nelems`
+ * elements, may be 0), `local_index` the device int64 holding the position of its extreme
+ * (result of dpb_search_over_axis), `index_offset` the flat index of the shard's first element
+ * in the whole array.  Writes the winning value to `out_value` (element of `typenum`) and its
+ * global flat index to `out_index` (int64), both in device memory; either may be NULL.  Rule:
+ * better value; equal values -> smaller index; NaN is extreme.  A rank with an empty shard
+ * takes part in the exchange and contributes nothing. */
+int dpb_comm_arg_extreme(void *comm, int typenum, int is_max, const void *src, int64_t nelems,
+                         const void *local_index, int64_t index_offset, void *out_value,
+                         void *out_index, void *stream);
+
 /* --------------------------------------------------------- introspection  */
 /* Name of the kernel family chosen by the most recent dispatch-level call in
  * this thread ("binary_contig_vec", "strided_rows", "transpose_tile", ...),
