@@ -410,6 +410,14 @@ def run_gpu_arm(args):
         e2e_step()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     e2e_ms = max_over_ranks(e2e_wall_ms)
+    # what came back to the host must satisfy put-call parity on the inputs that went out:
+    # call - put = P - S * exp(-r T)  (a property of the chain, checked on a strided sample)
+    sl = slice(0, n, 4099)
+    lhs = ho[0].array[sl] - ho[1].array[sl]
+    rhs = hp[0].array[sl] - hp[1].array[sl] * np.exp(-RATE * hp[2].array[sl])
+    e2e_check = bool(np.allclose(lhs, rhs, rtol=1e-11, atol=1e-11))
+    if not e2e_check:
+        raise RuntimeError("end-to-end outputs violate put-call parity")
     # what the links alone allow, all ranks copying at once and no kernel running: both directions
     # together (the step's copies) and each direction on its own
     copy_ms = wall_ms(lambda: e2e_step(compute=False))
@@ -423,14 +431,6 @@ def run_gpu_arm(args):
            "per_rank_d2h_gbs_alone": 2 * 8 * n / (d2h_ms * 1e-3) / 1e9,
            "host_cores_of_rank0": len(os.sched_getaffinity(0)),
            }
-    # what came back to the host must satisfy put-call parity on the inputs that went out:
-    # call - put = P - S * exp(-r T)  (a property of the chain, checked on a strided sample)
-    sl = slice(0, n, 4099)
-    lhs = ho[0].array[sl] - ho[1].array[sl]
-    rhs = hp[0].array[sl] - hp[1].array[sl] * np.exp(-RATE * hp[2].array[sl])
-    e2e_check = bool(np.allclose(lhs, rhs, rtol=1e-11, atol=1e-11))
-    if not e2e_check:
-        raise RuntimeError("end-to-end outputs violate put-call parity")
     del chunk_bufs
     for b in hp + ho:
         b.free()

@@ -389,8 +389,7 @@ int dpb_comm_extreme(void *comm, int typenum, int is_max, const void *partial, v
     if (!c) return set_error(DPB_ERR_VALUE, "not a communicator");
     if (count < 0 || (count > 0 && (!partial || !out))) return set_error(DPB_ERR_VALUE, "dpb_comm_extreme: bad arguments");
     if (count == 0) return DPB_OK;
-    if (typenum == DPB_CFLOAT || typenum == DPB_CDOUBLE || type_size(typenum) == 0)
-        return set_error(DPB_ERR_TYPE, "dpb_comm_extreme: type %s is not ordered here", type_name(typenum));
+    if (type_size(typenum) == 0) return set_error(DPB_ERR_TYPE, "dpb_comm_extreme: unknown type %d", typenum);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     DPB_TRY(gather_bytes(c, partial, static_cast<size_t>(count) * type_size(typenum), s));
     switch (typenum) {
@@ -410,6 +409,8 @@ int dpb_comm_extreme(void *comm, int typenum, int is_max, const void *partial, v
         DPB_CASE(DPB_HALF, half_t)
         DPB_CASE(DPB_FLOAT, float)
         DPB_CASE(DPB_DOUBLE, double)
+        DPB_CASE(DPB_CFLOAT, cfloat)
+        DPB_CASE(DPB_CDOUBLE, cdouble)
 #undef DPB_CASE
     default: return set_error(DPB_ERR_TYPE, "dpb_comm_extreme: unknown type %d", typenum);
     }

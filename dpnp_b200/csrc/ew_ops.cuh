@@ -9,6 +9,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "ew_complex.cuh"
 
 namespace dpb {
 
@@ -72,32 +73,35 @@ template <class T> struct AbsOp {
     }
 };
 
-#define DPB_FP_UNARY(NAME, FN_F, FN_D)                                           \
+// floating and complex arguments; float16 is computed in float32
+#define DPB_FP_UNARY(NAME, FN_F, FN_D, FN_C)                                     \
     template <class T> struct NAME {                                             \
-        using R = std::conditional_t<is_fp_v<T>, T, NoType>;                     \
+        using R = std::conditional_t<is_fp_v<T> || is_cplx_v<T>, T, NoType>;     \
         static DPB_D R apply(T x)                                                \
         {                                                                        \
-            if constexpr (std::is_same_v<T, double>) return FN_D(x);             \
+            if constexpr (is_cplx_v<T>) return cx::FN_C(x);                      \
+            else if constexpr (std::is_same_v<T, double>) return FN_D(x);        \
             else if constexpr (std::is_same_v<T, float>) return FN_F(x);         \
             else return __float2half(FN_F(__half2float(x)));                     \
         }                                                                        \
     };
 
-DPB_FP_UNARY(ExpOp, expf, exp)
-DPB_FP_UNARY(LogOp, logf, log)
-DPB_FP_UNARY(SqrtOp, sqrtf, sqrt)
-DPB_FP_UNARY(SinOp, sinf, sin)
-DPB_FP_UNARY(CosOp, cosf, cos)
-DPB_FP_UNARY(TanhOp, tanhf, tanh)
-DPB_FP_UNARY(Expm1Op, expm1f, expm1)
-DPB_FP_UNARY(Log1pOp, log1pf, log1p)
+DPB_FP_UNARY(ExpOp, expf, exp, c_exp)         // exp.hpp:63-133
+DPB_FP_UNARY(LogOp, logf, log, c_log)         // log.hpp:60-84
+DPB_FP_UNARY(SqrtOp, sqrtf, sqrt, c_sqrt)     // sqrt.hpp:62-84
+DPB_FP_UNARY(SinOp, sinf, sin, c_sin)         // sin.hpp
+DPB_FP_UNARY(CosOp, cosf, cos, c_cos)         // cos.hpp:65-180
+DPB_FP_UNARY(TanhOp, tanhf, tanh, c_tanh)     // tanh.hpp
+DPB_FP_UNARY(Expm1Op, expm1f, expm1, c_expm1) // expm1.hpp:78-141
+DPB_FP_UNARY(Log1pOp, log1pf, log1p, c_log1p) // log1p.hpp
 #undef DPB_FP_UNARY
 
 template <class T> struct ReciprocalOp {
-    using R = std::conditional_t<is_fp_v<T>, T, NoType>;
+    using R = std::conditional_t<is_fp_v<T> || is_cplx_v<T>, T, NoType>;
     static DPB_D R apply(T x)
     {
-        if constexpr (is_half_v<T>) return __float2half(1.0f / __half2float(x));
+        if constexpr (is_cplx_v<T>) return cx::c_reciprocal(x);
+        else if constexpr (is_half_v<T>) return __float2half(1.0f / __half2float(x));
         else return T(1) / x;
     }
 };
@@ -146,10 +150,11 @@ template <class T> struct CeilOp {
 };
 
 template <class T> struct SignOp {
-    using R = std::conditional_t<is_bool_v<T> || is_cplx_v<T>, NoType, T>;
+    using R = std::conditional_t<is_bool_v<T>, NoType, T>;
     static DPB_D R apply(T x)
     {
-        if constexpr (is_uint_v<T>) return static_cast<T>(x > 0 ? 1 : 0);
+        if constexpr (is_cplx_v<T>) return cx::c_sign(x);
+        else if constexpr (is_uint_v<T>) return static_cast<T>(x > 0 ? 1 : 0);
         else if constexpr (is_sint_v<T>) return static_cast<T>((x > 0) - (x < 0));
         else {
             auto v = up(x);
@@ -232,23 +237,29 @@ template <class A, class B> struct MultiplyOp {
     }
 };
 
-// true_divide: floating types only (integers are promoted to the default
+// true_divide: floating and complex types (integers are promoted to the default
 // floating type by the caller, dpnp/tensor/_type_utils.py:89-107).
 template <class A, class B> struct TrueDivideOp {
-    using R = std::conditional_t<std::is_same_v<A, B> && is_fp_v<A>, A, NoType>;
+    using R = std::conditional_t<std::is_same_v<A, B> && (is_fp_v<A> || is_cplx_v<A>), A, NoType>;
     static DPB_D R apply(A a, B b)
     {
-        if constexpr (is_half_v<A>) return __float2half(__half2float(a) / __half2float(b));
+        // complex quotients (true_divide.hpp:62-113; a real operand next to a complex one is
+        // promoted by the caller, which gives the same value as the mixed kernels of the reference)
+        if constexpr (is_cplx_v<A>) return cx::c_div(a, b);
+        else if constexpr (is_half_v<A>) return __float2half(__half2float(a) / __half2float(b));
         else return a / b;
     }
 };
 
 // maximum / minimum propagate NaN (first NaN operand wins).
+// Complex operands: the first one wins if it holds a NaN or is greater in the (real, imaginary)
+// order, else the second (utils/math_utils.hpp:99-131: max_complex / min_complex).
 template <class A, class B> struct MaximumOp {
-    using R = std::conditional_t<std::is_same_v<A, B> && !is_cplx_v<A>, A, NoType>;
+    using R = std::conditional_t<std::is_same_v<A, B>, A, NoType>;
     static DPB_D R apply(A a, B b)
     {
-        if constexpr (is_bool_v<A>) return bool_t(a.v || b.v);
+        if constexpr (is_cplx_v<A>) return (is_nan(a) || cx::c_less(b, a)) ? a : b;
+        else if constexpr (is_bool_v<A>) return bool_t(a.v || b.v);
         else if constexpr (is_fp_v<A>) {
             auto x = up(a), y = up(b);
             return (x != x || x >= y) ? a : b;
@@ -258,10 +269,11 @@ template <class A, class B> struct MaximumOp {
 };
 
 template <class A, class B> struct MinimumOp {
-    using R = std::conditional_t<std::is_same_v<A, B> && !is_cplx_v<A>, A, NoType>;
+    using R = std::conditional_t<std::is_same_v<A, B>, A, NoType>;
     static DPB_D R apply(A a, B b)
     {
-        if constexpr (is_bool_v<A>) return bool_t(a.v && b.v);
+        if constexpr (is_cplx_v<A>) return (is_nan(a) || cx::c_less(a, b)) ? a : b;
+        else if constexpr (is_bool_v<A>) return bool_t(a.v && b.v);
         else if constexpr (is_fp_v<A>) {
             auto x = up(a), y = up(b);
             return (x != x || x <= y) ? a : b;
@@ -291,12 +303,20 @@ template <int K, class X, class Y> DPB_D bool cmp_scalar(X x, Y y)
 
 template <int K, class A, class B> struct CompareOp {
     static constexpr bool ordered = (K != CMP_EQ && K != CMP_NE);
-    using R = std::conditional_t<cmp_pair_v<A, B> && !(ordered && is_cplx_v<A>), bool_t, NoType>;
+    using R = std::conditional_t<cmp_pair_v<A, B>, bool_t, NoType>;
     static DPB_D R apply(A a, B b)
     {
         if constexpr (is_cplx_v<A>) {
-            bool eq = (a.re == b.re) && (a.im == b.im);
-            return bool_t(K == CMP_EQ ? eq : !eq);
+            // ordered comparisons of complex numbers: real parts decide unless equal, then the
+            // imaginary parts; false whenever a NaN is involved (less.hpp:60-101)
+            if constexpr (K == CMP_LT) return bool_t(cx::c_less(a, b));
+            else if constexpr (K == CMP_LE) return bool_t(cx::c_less_equal(a, b));
+            else if constexpr (K == CMP_GT) return bool_t(cx::c_less(b, a));
+            else if constexpr (K == CMP_GE) return bool_t(cx::c_less_equal(b, a));
+            else {
+                bool eq = (a.re == b.re) && (a.im == b.im);
+                return bool_t(K == CMP_EQ ? eq : !eq);
+            }
         }
         else if constexpr (is_bool_v<A>) {
             return bool_t(cmp_scalar<K>(int(a.v != 0), int(b.v != 0)));
@@ -338,12 +358,27 @@ template <class A, class B> struct LogicalOrOp {
     }
 };
 
-// pow: floating types only in this build
+// pow (pow.hpp:63-114): integers by repeated squaring with wrap-around, a negative exponent gives
+// 0; floating types through the library pow; complex through integer powers / exp(b log a)
 template <class A, class B> struct PowOp {
-    using R = std::conditional_t<std::is_same_v<A, B> && is_fp_v<A>, A, NoType>;
+    using R = std::conditional_t<std::is_same_v<A, B> && (is_fp_v<A> || is_int_v<A> || is_cplx_v<A>), A, NoType>;
     static DPB_D R apply(A a, B b)
     {
-        if constexpr (std::is_same_v<A, double>) return pow(a, b);
+        if constexpr (is_int_v<A>) {
+            if constexpr (std::is_signed_v<B>) { if (b < B(0)) return A(0); }
+            using U = std::make_unsigned_t<A>;
+            U base = static_cast<U>(a), res = 1;
+            if (a == A(1) || b == B(0)) return A(1);
+            std::make_unsigned_t<B> e = static_cast<std::make_unsigned_t<B>>(b);
+            while (e > 0) {
+                if (e & 1) res = static_cast<U>(res * base);
+                e >>= 1;
+                base = static_cast<U>(base * base);
+            }
+            return static_cast<A>(res);
+        }
+        else if constexpr (is_cplx_v<A>) return cx::c_pow(a, b);
+        else if constexpr (std::is_same_v<A, double>) return pow(a, b);
         else if constexpr (std::is_same_v<A, float>) return powf(a, b);
         else return __float2half(powf(__half2float(a), __half2float(b)));
     }
@@ -362,22 +397,35 @@ template <class A, class B> struct PowOp {
             else { const float x = __half2float(v); return __float2half(EXPR_F); } \
         }                                                                        \
     };
+// the same with a complex branch
+#define DPB_FP_UNARY2C(NAME, EXPR_F, EXPR_D, FN_C)                               \
+    template <class T> struct NAME {                                             \
+        using R = std::conditional_t<is_fp_v<T> || is_cplx_v<T>, T, NoType>;     \
+        static DPB_D R apply(T v)                                                \
+        {                                                                        \
+            if constexpr (is_cplx_v<T>) return cx::FN_C(v);                      \
+            else if constexpr (std::is_same_v<T, double>) { const double x = v; return (EXPR_D); } \
+            else if constexpr (std::is_same_v<T, float>) { const float x = v; return (EXPR_F); } \
+            else { const float x = __half2float(v); return __float2half(EXPR_F); } \
+        }                                                                        \
+    };
 
-DPB_FP_UNARY2(AcosOp, acosf(x), acos(x))        // acos.hpp
-DPB_FP_UNARY2(AcoshOp, acoshf(x), acosh(x))     // acosh.hpp
-DPB_FP_UNARY2(AsinOp, asinf(x), asin(x))        // asin.hpp
-DPB_FP_UNARY2(AsinhOp, asinhf(x), asinh(x))     // asinh.hpp
-DPB_FP_UNARY2(AtanOp, atanf(x), atan(x))        // atan.hpp
-DPB_FP_UNARY2(AtanhOp, atanhf(x), atanh(x))     // atanh.hpp
-DPB_FP_UNARY2(CbrtOp, cbrtf(x), cbrt(x))        // cbrt.hpp
-DPB_FP_UNARY2(CoshOp, coshf(x), cosh(x))        // cosh.hpp
-DPB_FP_UNARY2(SinhOp, sinhf(x), sinh(x))        // sinh.hpp
-DPB_FP_UNARY2(TanOp, tanf(x), tan(x))           // tan.hpp
-DPB_FP_UNARY2(Exp2Op, exp2f(x), exp2(x))        // exp2.hpp
-DPB_FP_UNARY2(Log2Op, log2f(x), log2(x))        // log2.hpp
-DPB_FP_UNARY2(Log10Op, log10f(x), log10(x))     // log10.hpp
+DPB_FP_UNARY2C(AcosOp, acosf(x), acos(x), c_acos)       // acos.hpp
+DPB_FP_UNARY2C(AcoshOp, acoshf(x), acosh(x), c_acosh)   // acosh.hpp
+DPB_FP_UNARY2C(AsinOp, asinf(x), asin(x), c_asin)       // asin.hpp
+DPB_FP_UNARY2C(AsinhOp, asinhf(x), asinh(x), c_asinh)   // asinh.hpp
+DPB_FP_UNARY2C(AtanOp, atanf(x), atan(x), c_atan)       // atan.hpp
+DPB_FP_UNARY2C(AtanhOp, atanhf(x), atanh(x), c_atanh)   // atanh.hpp
+DPB_FP_UNARY2(CbrtOp, cbrtf(x), cbrt(x))                // cbrt.hpp
+DPB_FP_UNARY2C(CoshOp, coshf(x), cosh(x), c_cosh)       // cosh.hpp
+DPB_FP_UNARY2C(SinhOp, sinhf(x), sinh(x), c_sinh)       // sinh.hpp
+DPB_FP_UNARY2C(TanOp, tanf(x), tan(x), c_tan)           // tan.hpp
+DPB_FP_UNARY2C(Exp2Op, exp2f(x), exp2(x), c_exp2)       // exp2.hpp
+DPB_FP_UNARY2C(Log2Op, log2f(x), log2(x), c_log2)       // log2.hpp
+DPB_FP_UNARY2C(Log10Op, log10f(x), log10(x), c_log10)   // log10.hpp
 // rsqrt.hpp: reciprocal of the correctly rounded square root
 DPB_FP_UNARY2(RsqrtOp, 1.0f / sqrtf(x), 1.0 / sqrt(x))
+#undef DPB_FP_UNARY2C
 #undef DPB_FP_UNARY2
 
 // trunc.hpp / round.hpp (round half to even): identity on integers

@@ -1,10 +1,10 @@
-// Max and min reductions (same input and output type; complex is not ordered).
+// Max and min reductions (same input and output type; complex values in the (real, imaginary) order).
 #include "reduce_register.cuh"
 namespace dpb {
 template <int TN> static void reg_minmax_one(RedTables &t)
 {
     using T = type_of_t<TN>;
-    if constexpr (!is_cplx_v<T>) {
+    {
         t.reduce[DPB_R_MAX][TN][TN] = &red_entry<ExtremeRed<true, T, T>>;
         t.reduce[DPB_R_MIN][TN][TN] = &red_entry<ExtremeRed<false, T, T>>;
     }

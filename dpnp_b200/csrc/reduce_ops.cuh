@@ -31,14 +31,16 @@ template <class Out> using acc_of_t = typename acc_of<Out>::type;
 
 template <class T> DPB_HD T lowest_value()
 {
-    if constexpr (std::is_same_v<T, float>) return -INFINITY;
+    if constexpr (is_cplx_v<T>) return T(lowest_value<real_of_t<T>>(), lowest_value<real_of_t<T>>());
+    else if constexpr (std::is_same_v<T, float>) return -INFINITY;
     else if constexpr (std::is_same_v<T, double>) return -static_cast<double>(INFINITY);
     else if constexpr (is_bool_v<T>) return bool_t(false);
     else return std::numeric_limits<T>::lowest();
 }
 template <class T> DPB_HD T highest_value()
 {
-    if constexpr (std::is_same_v<T, float>) return INFINITY;
+    if constexpr (is_cplx_v<T>) return T(highest_value<real_of_t<T>>(), highest_value<real_of_t<T>>());
+    else if constexpr (std::is_same_v<T, float>) return INFINITY;
     else if constexpr (std::is_same_v<T, double>) return static_cast<double>(INFINITY);
     else if constexpr (is_bool_v<T>) return bool_t(true);
     else return std::numeric_limits<T>::max();
@@ -122,6 +124,29 @@ template <class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct HypotRed {
 };
 
 // ------------------------------------------------------------ max and min
+// Order helpers shared by max/min and the searches.  Complex values compare by real part, then by
+// imaginary part, and a NaN in either part makes the value the extreme
+// (include/utils/math_utils.hpp:43-131, include/kernels/reductions.hpp:1914-1963).
+template <class V> DPB_D bool sv_nan(const V &v)
+{
+    if constexpr (is_cplx_v<V>) return v.re != v.re || v.im != v.im;
+    else if constexpr (std::is_floating_point_v<V>) return v != v;
+    else return false;
+}
+template <class V> DPB_D bool sv_eq(const V &a, const V &b)
+{
+    if constexpr (is_cplx_v<V>) return a.re == b.re && a.im == b.im;
+    else return a == b;
+}
+template <bool IS_MAX, class V> DPB_D bool sv_better(const V &a, const V &b)   // NaN-free operands
+{
+    if constexpr (is_cplx_v<V>) {
+        if (a.re == b.re) return IS_MAX ? (a.im > b.im) : (a.im < b.im);
+        return IS_MAX ? (a.re > b.re) : (a.re < b.re);
+    }
+    else return IS_MAX ? (a > b) : (a < b);
+}
+
 template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struct ExtremeRed {
     using In = TIn;
     using Acc = TAcc;
@@ -134,10 +159,10 @@ template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struc
     static DPB_D Acc combine(Acc a, Acc b)
     {
         if constexpr (is_bool_v<Acc>) return IS_MAX ? bool_t(a.v || b.v) : bool_t(a.v && b.v);
-        else if constexpr (std::is_floating_point_v<Acc>) {
-            if (a != a) return a;
-            if (b != b) return b;
-            return IS_MAX ? (a > b ? a : b) : (a < b ? a : b);
+        else if constexpr (std::is_floating_point_v<Acc> || is_cplx_v<Acc>) {
+            if (sv_nan(a)) return a;
+            if (sv_nan(b)) return b;
+            return sv_better<IS_MAX>(a, b) ? a : b;
         }
         else return IS_MAX ? (a > b ? a : b) : (a < b ? a : b);
     }
@@ -154,15 +179,15 @@ template <class V> struct alignas(16) ValIdx {
 // among NaNs) the smaller index wins.
 template <bool IS_MAX, class V> DPB_D bool search_better(const ValIdx<V> &a, const ValIdx<V> &b)
 {
-    if constexpr (std::is_floating_point_v<V>) {
-        const bool an = a.val != a.val, bn = b.val != b.val;
+    if constexpr (std::is_floating_point_v<V> || is_cplx_v<V>) {
+        const bool an = sv_nan(a.val), bn = sv_nan(b.val);
         if (an || bn) {
             if (an && bn) return a.idx < b.idx;
             return an;
         }
     }
-    if (a.val == b.val) return a.idx < b.idx;
-    return IS_MAX ? (a.val > b.val) : (a.val < b.val);
+    if (sv_eq(a.val, b.val)) return a.idx < b.idx;
+    return sv_better<IS_MAX>(a.val, b.val);
 }
 
 template <class V> struct search_val { using type = V; };
@@ -210,8 +235,12 @@ struct SearchRed {
             V x;
             if constexpr (is_bool_v<TIn>) x = v.v ? 1 : 0;
             else x = convert<V>(v);
-            bool wins = IS_MAX ? (x > a.val) : (x < a.val);
-            if constexpr (std::is_floating_point_v<V>) wins = wins || (x != x && !(a.val != a.val));
+            bool wins;
+            if constexpr (std::is_floating_point_v<V> || is_cplx_v<V>) {
+                const bool xn = sv_nan(x), an = sv_nan(a.val);
+                wins = an ? false : (xn || sv_better<IS_MAX>(x, a.val));
+            }
+            else wins = sv_better<IS_MAX>(x, a.val);
             wins = wins || (a.idx == std::numeric_limits<int64_t>::max());
             Acc r = a;
             if (wins) {
@@ -226,25 +255,33 @@ struct SearchRed {
     // a mere tie) are the elements examined one by one.
     template <int N> static DPB_D Acc step_vec(const Acc &a, const In (&v)[N], int64_t i0)
     {
-        V x[N];
-        bool any_nan = false;
-#pragma unroll
-        for (int k = 0; k < N; ++k) {
-            if constexpr (is_bool_v<TIn>) x[k] = v[k].v ? 1 : 0;
-            else x[k] = convert<V>(v[k]);
-            if constexpr (std::is_floating_point_v<V>) any_nan = any_nan || (x[k] != x[k]);
-        }
-        V m = x[0];
-#pragma unroll
-        for (int k = 1; k < N; ++k) m = IS_MAX ? (x[k] > m ? x[k] : m) : (x[k] < m ? x[k] : m);
-        const bool maybe = (IS_MAX ? (m > a.val) : (m < a.val)) || any_nan ||
-                           (a.idx == std::numeric_limits<int64_t>::max());
-        Acc r = a;
-        if (maybe) {
+        if constexpr (is_cplx_v<V>) {
+            Acc r = a;
 #pragma unroll
             for (int k = 0; k < N; ++k) r = step(r, v[k], i0 + k);
+            return r;
         }
-        return r;
+        else {
+            V x[N];
+            bool any_nan = false;
+#pragma unroll
+            for (int k = 0; k < N; ++k) {
+                if constexpr (is_bool_v<TIn>) x[k] = v[k].v ? 1 : 0;
+                else x[k] = convert<V>(v[k]);
+                if constexpr (std::is_floating_point_v<V>) any_nan = any_nan || (x[k] != x[k]);
+            }
+            V m = x[0];
+#pragma unroll
+            for (int k = 1; k < N; ++k) m = IS_MAX ? (x[k] > m ? x[k] : m) : (x[k] < m ? x[k] : m);
+            const bool maybe = (IS_MAX ? (m > a.val) : (m < a.val)) || any_nan ||
+                               (a.idx == std::numeric_limits<int64_t>::max());
+            Acc r = a;
+            if (maybe) {
+#pragma unroll
+                for (int k = 0; k < N; ++k) r = step(r, v[k], i0 + k);
+            }
+            return r;
+        }
     }
     static DPB_D Acc combine(const Acc &a, const Acc &b) { return search_better<IS_MAX>(a, b) ? a : b; }
     static DPB_D Out finish(const Acc &a) { return a.idx; }

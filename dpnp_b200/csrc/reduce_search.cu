@@ -4,7 +4,7 @@ namespace dpb {
 template <int TN> static void reg_search_one(RedTables &t)
 {
     using T = type_of_t<TN>;
-    if constexpr (!is_cplx_v<T>) {
+    {
         t.search[DPB_S_ARGMAX][TN] = &red_entry<SearchRed<true, T>>;
         t.search[DPB_S_ARGMIN][TN] = &red_entry<SearchRed<false, T>>;
     }
