@@ -111,6 +111,7 @@ PROTOTYPES = {
     "dpb_event_destroy": (_i, [_vp]),
     "dpb_event_record": (_i, [_vp, _vp]),
     "dpb_event_synchronize": (_i, [_vp]),
+    "dpb_stream_wait_event": (_i, [_vp, _vp]),
     "dpb_event_elapsed_ms": (_i, [_vp, _vp, C.POINTER(C.c_float)]),
     "dpb_malloc": (_i, [_sz, _vp, _pvp]),
     "dpb_free": (_i, [_vp, _vp]),

@@ -207,6 +207,12 @@ int dpb_event_record(void *event, void *stream)
     return DPB_OK;
 }
 
+int dpb_stream_wait_event(void *stream, void *event)
+{
+    DPB_CUDA_TRY(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+    return DPB_OK;
+}
+
 int dpb_event_synchronize(void *event)
 {
     DPB_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));

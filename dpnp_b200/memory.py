@@ -232,9 +232,27 @@ class PinnedHostBuffer:
         self.free()
 
 
+def _order_after(owner_queue, other_queue):
+    """Make the work queued later on `owner_queue` (in particular the release of a block it owns)
+    wait for what has just been queued on `other_queue`."""
+    if other_queue is owner_queue or (other_queue.device == owner_queue.device
+                                      and other_queue.stream == owner_queue.stream):
+        return
+    other_queue.activate()
+    ev = C.c_void_p()
+    check(lib.dpb_event_create(C.byref(ev)))
+    try:
+        check(lib.dpb_event_record(ev, C.c_void_p(other_queue.stream)))
+        check(lib.dpb_stream_wait_event(C.c_void_p(owner_queue.stream), ev))
+    finally:
+        lib.dpb_event_destroy(ev)
+
+
 def copy_host_to_device(dst, host_array, queue=None):
     """Enqueue dst[...] = host_array (same dtype, both C-contiguous) without synchronising;
-    the host buffer must stay alive until the queue has been waited on."""
+    the host buffer must stay alive until the queue has been waited on.  With a `queue` other
+    than the array's own, the array's queue is made to wait for the copy, so that the memory
+    cannot return to the pool (freeing is ordered on the owning queue) while the copy runs."""
     u = dst.get_array() if hasattr(dst, "get_array") else dst
     q = queue or u.sycl_queue
     if not (u.flags.c_contiguous and host_array.flags.c_contiguous and u.dtype == host_array.dtype
@@ -243,6 +261,7 @@ def copy_host_to_device(dst, host_array, queue=None):
     q.activate()
     check(lib.dpb_memcpy(C.c_void_p(u._ptr), C.c_void_p(host_array.ctypes.data), host_array.nbytes, 0,
                          C.c_void_p(q.stream)))
+    _order_after(u.sycl_queue, q)
 
 
 def copy_device_to_host(host_array, src, queue=None):
@@ -255,6 +274,7 @@ def copy_device_to_host(host_array, src, queue=None):
     q.activate()
     check(lib.dpb_memcpy(C.c_void_p(host_array.ctypes.data), C.c_void_p(u._ptr), host_array.nbytes, 1,
                          C.c_void_p(q.stream)))
+    _order_after(u.sycl_queue, q)
 
 
 def create_data(x):

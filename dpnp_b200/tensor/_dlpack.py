@@ -13,6 +13,8 @@ import ctypes as C
 
 import numpy as np
 
+from .. import _lib
+
 kDLCPU, kDLCUDA, kDLCUDAHost, kDLCUDAManaged = 1, 2, 3, 13
 _CODES = {"i": 0, "u": 1, "f": 2, "c": 5, "b": 6}     # DLDataTypeCode: int, uint, float, complex, bool
 
@@ -119,11 +121,24 @@ def from_dlpack(obj, /, *, device=None, copy=None):
     from ..memory import StreamQueue, get_default_queue
     from ._usmarray import usm_ndarray
 
+    q = device if isinstance(device, StreamQueue) else None
     if hasattr(obj, "__dlpack__"):
+        # The producer is handed the stream the array will be used on, so that it orders its
+        # pending work before this library's first kernel (the stream is a non-blocking one: it
+        # does not wait for the legacy default stream by itself).  A producer that does not
+        # take the argument gets a device-wide synchronisation instead.  Capsules passed in
+        # directly carry no such handshake: their producer's work is the caller's to order.
+        if q is None:
+            try:
+                q = get_default_queue(int(obj.__dlpack_device__()[1]))
+            except Exception:
+                q = get_default_queue()
         try:
-            capsule = obj.__dlpack__(stream=-1)          # no synchronisation requested
-        except TypeError:
+            capsule = obj.__dlpack__(stream=q.stream)
+        except (TypeError, ValueError, AssertionError, RuntimeError, BufferError):
             capsule = obj.__dlpack__()
+            q.activate()
+            _lib.check(_lib.lib.dpb_device_synchronize())
     else:
         capsule = obj
     if not _api.PyCapsule_IsValid(capsule, _NAME):
@@ -156,7 +171,8 @@ def from_dlpack(obj, /, *, device=None, copy=None):
     lo = sum(min(0, (n - 1) * s) for n, s in zip(shape, strides)) if all(shape) else 0
     hi = sum(max(0, (n - 1) * s) for n, s in zip(shape, strides)) if all(shape) else 0
     owner = _Imported(managed, (hi - lo + 1) * dt.itemsize if all(shape) else 0, ptr + lo * dt.itemsize)
-    q = device if isinstance(device, StreamQueue) else get_default_queue(t.device.device_id)
+    if q is None or q.device != t.device.device_id:
+        q = get_default_queue(t.device.device_id)
     owner.sycl_queue = q
     res = usm_ndarray._view(owner, ptr, shape, strides, dt, q)
     if copy:

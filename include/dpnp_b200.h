@@ -234,6 +234,9 @@ int dpb_event_create(void **event);
 int dpb_event_destroy(void *event);
 int dpb_event_record(void *event, void *stream);
 int dpb_event_synchronize(void *event);
+/* Work queued on `stream` after this call waits for `event` (cudaStreamWaitEvent): the explicit
+ * form of the `depends` event lists of the reference's calls, needed only between two queues. */
+int dpb_stream_wait_event(void *stream, void *event);
 int dpb_event_elapsed_ms(void *start, void *stop, float *ms);
 
 /* ------------------------------------------------------------- allocator */
@@ -386,7 +389,10 @@ int dpb_reduce_strided(int op, int t_in, int t_out, int64_t iter_nelems, int64_t
  * (cudaGetSymbolAddress, with that device current); make that first call before starting
  * any stream capture.  All calls share the one array, which keeps whatever the previous
  * call left there: nothing needs clearing, because every partial is written before it is
- * read, but two calls that overlap on the GPU (different streams) race on it. */
+ * read, but two calls that overlap on the GPU (different streams) race on it.  The
+ * address found on the first call is remembered per device ordinal (up to 64 devices) for
+ * the life of the process; a program that calls cudaDeviceReset must not use this entry
+ * point afterwards. */
 int dpb_reduce_axis1_contig_noalloc(int op, int t_in, int t_out, int64_t iter_nelems,
                                     int64_t reduction_nelems, const void *arg, int64_t arg_off,
                                     void *res, int64_t res_off, void *stream);

@@ -68,6 +68,16 @@ def parts_close(got, exp, tol):
     return ok
 
 
+def modulus_close(got, exp, tol):
+    """|got - exp| <= tol + tol |exp| on the complex values, which is what assert_allclose does
+    with complex arrays in the reference's tests (NaNs in the same places)."""
+    nan_g = np.isnan(got.real) | np.isnan(got.imag)
+    nan_e = np.isnan(exp.real) | np.isnan(exp.imag)
+    with np.errstate(all="ignore"):
+        ok = np.abs(got - exp) <= tol + tol * np.abs(exp)
+    return np.where(nan_g | nan_e, nan_g == nan_e, ok | (got == exp))
+
+
 def expected(name, z):
     with warnings.catch_warnings(), np.errstate(all="ignore"):
         warnings.simplefilter("ignore")
@@ -162,9 +172,9 @@ def test_division_powers_and_ordering(lib, dt):
         assert parts_close(run_binary(lib, 0, zc, zd), zc / zd, 4 * res).all()
         zs = (rng.uniform(-3, 3, 5000) + 1j * rng.uniform(-3, 3, 5000)).astype(dt)
         zt = (rng.uniform(-3, 3, 5000) + 1j * rng.uniform(-3, 3, 5000)).astype(dt)
-        assert parts_close(run_binary(lib, 1, zs, zt), np.power(zs, zt), 50 * res).all()
+        assert modulus_close(run_binary(lib, 1, zs, zt), np.power(zs, zt), 50 * res).all()
         ints = np.array([complex(k, 0) for k in rng.integers(-6, 7, 5000)], dtype=dt)
-        assert parts_close(run_binary(lib, 1, zs, ints), np.power(zs, ints), 50 * res).all()
+        assert modulus_close(run_binary(lib, 1, zs, ints), np.power(zs, ints), 50 * res).all()
         got = run_binary(lib, 2, a, b)                  # (less, less_equal) in the two parts
         # NumPy orders complex numbers the same way except next to NaNs, where every ordered
         # comparison here is false (utils/math_utils.hpp:43-97 of the reference)

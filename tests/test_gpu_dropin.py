@@ -1,9 +1,35 @@
 """User code written against dpnp runs unchanged: `import dpnp as np`."""
 
+import os
+import runpy
+
 import numpy
 import pytest
 
 pytestmark = pytest.mark.gpu
+
+# where a checkout of the reference lies, if there is one on this machine
+REFERENCE_ROOT = os.environ.get("DPNP_REFERENCE_ROOT", "/root/reference")
+
+
+def test_the_reference_example_file_runs_as_it_is(capsys):
+    """examples/example_bs.py of the reference, executed unmodified with `dpnp` resolving to this
+    library (skipped where no checkout of the reference is present)."""
+    path = os.path.join(REFERENCE_ROOT, "examples", "example_bs.py")
+    if not os.path.exists(path):
+        pytest.skip("no checkout of the reference on this machine")
+    import dpnp_b200
+
+    ns = runpy.run_path(path, run_name="__main__")
+    assert ns["np"] is dpnp_b200
+    call, put = ns["call"], ns["put"]
+    from oracle import dpnp_oracle as orc
+
+    ec, ep = orc.black_scholes_chain(ns["price"].asnumpy(), ns["strike"].asnumpy(), ns["t"].asnumpy(),
+                                     ns["RISK_FREE"], ns["VOLATILITY"])
+    numpy.testing.assert_allclose(call.asnumpy(), ec, rtol=1e-13, atol=1e-12)
+    numpy.testing.assert_allclose(put.asnumpy(), ep, rtol=1e-13, atol=1e-12)
+    assert capsys.readouterr().out.count("[") >= 2
 
 
 def test_example_style_program_runs_under_the_dpnp_name():
