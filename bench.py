@@ -512,7 +512,7 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
     pp, ps, pt = (a.get_array()._ptr for a in (price, strike, tt))
     pc, pq = call.get_array()._ptr, put.get_array()._ptr
     ms = median_time_ms(ev, lambda: lib.dpb_black_scholes_f64(n, pp, ps, pt, RATE, VOL, pc, pq, S), 10, batch=4)
-    rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms, "black_scholes_f64",
+    rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms, "black_scholes_f64",
         "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option")
 
     # the same chain through the general front-end: traced once, then one interpreted launch
@@ -520,7 +520,7 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
     ms = median_time_ms(ev, lambda: chain(price, strike, tt, call, put), 10, batch=4)
     if chain.fused_calls == 0:
         raise RuntimeError(f"the Black-Scholes chain was not fused: {chain.last_reason}")
-    rec("c2_black_scholes_fuse_decorator_f64_2^26", n * BYTES_PER_OPTION_FUSED, ms,
+    rec("c2_black_scholes_fuse_decorator_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms,
         note="dpnp_b200.fuse: the 26-call chain as a register-machine program, one launch")
 
     # C1: add f32 2^24, rotating over 4 buffer sets (768 MiB > L2)
@@ -540,9 +540,9 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
         lib.dpb_binary_contig(0, 10, 10, 10, m, a.get_array()._ptr, 0, b.get_array()._ptr, 0, o.get_array()._ptr, 0, S)
 
     ms = median_time_ms(ev, lambda: [c1_api() for _ in range(8)], 10) / 8
-    rec("c1_add_f32_2^24_api", 12 * m, ms, note="8 back-to-back dpnp.add calls per sample, rotating buffers")
+    rec("c1_add_f32_2^24_api", 12 * m * world, ms, note="8 back-to-back dpnp.add calls per sample, rotating buffers")
     ms = median_time_ms(ev, lambda: [c1_abi() for _ in range(8)], 10) / 8
-    rec("c1_add_f32_2^24_c_abi", 12 * m, ms)
+    rec("c1_add_f32_2^24_c_abi", 12 * m * world, ms)
     del sets
 
     # further kernels of the path, one representative shape each (every rank runs its own copy);

@@ -47,6 +47,8 @@ struct DeviceProps {
 };
 const DeviceProps &device_props();
 int64_t tuning_ctas_per_sm();
+bool tuning_verbose();        // log every kernel choice on stderr
+bool tuning_force_generic();  // send every elementwise / reduction call to the generic strided kernels
 int64_t tuning_fused_elems();  // elements per thread and register of the fused-chain interpreter
 
 // ------------------------------------------------------------ element types

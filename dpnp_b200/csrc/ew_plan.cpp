@@ -66,6 +66,10 @@ int make_ew_plan(int narr, int nd, const int64_t *shape, const int64_t *strides,
     }
     for (int k = 0; k < narr; ++k) plan.offsets[k] = offs[k];
 
+    if (tuning_force_generic()) {   // debugging aid: the kernel with no layout assumptions
+        plan.kind = EW_GENERIC;
+        return DPB_OK;
+    }
     const int last = cnd - 1;
     // (1) one collapsed dimension, output dense, inputs dense or one element
     if (cnd == 1 && (plan.strides[out][0] == 1 || n == 1)) {

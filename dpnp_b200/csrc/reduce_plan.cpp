@@ -86,6 +86,10 @@ int make_red_plan(int iter_nd, const int64_t *iter_shape, const int64_t *iter_sr
     }
 
     if (nred == 0) return DPB_OK;
+    if (tuning_force_generic() && plan.iter_nd + plan.red_nd <= kMaxD) {
+        plan.kind = RED_GENERIC;
+        return DPB_OK;
+    }
     const bool outer_ok = plan.iter_nd >= 1 && plan.iter_src[plan.iter_nd - 1] == 1 &&
                           plan.iter_dst[plan.iter_nd - 1] == 1 && plan.iter_shape[plan.iter_nd - 1] >= 16;
     if (plan.red_nd == 0 || (plan.red_nd == 1 && plan.red_src[0] == 1)) {

@@ -1,6 +1,7 @@
 // Host runtime of libdpnp_b200: thread-local error state, device selection,
 // streams/events, the stream-ordered allocator and raw copies.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -23,10 +24,40 @@ int set_error(int status, const char *fmt, ...)
     return status;
 }
 
+// Run-time switches, read once from the environment (DPNP_B200_VERBOSE, DPNP_B200_FORCE_GENERIC;
+// the reference's counterparts are the DPNP_* / SYCL_* variables of dpnp/config.py:32-59) and
+// changeable through dpb_set_tuning("verbose" | "force_generic", 0 | 1).
+static int env_flag(const char *name)
+{
+    const char *v = getenv(name);
+    return (v && *v && std::strcmp(v, "0") != 0) ? 1 : 0;
+}
+static std::atomic<int> g_verbose{-1}, g_force_generic{-1};
+bool tuning_verbose()
+{
+    int v = g_verbose.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = env_flag("DPNP_B200_VERBOSE");
+        g_verbose.store(v);
+    }
+    return v != 0;
+}
+bool tuning_force_generic()
+{
+    int v = g_force_generic.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = env_flag("DPNP_B200_FORCE_GENERIC");
+        g_force_generic.store(v);
+    }
+    return v != 0;
+}
+
 void note_kernel(const char *name)
 {
     g_last_kernel = name;
     ++g_launches;
+    if (tuning_verbose())
+        fprintf(stderr, "[dpnp_b200] launch %lld of this thread: %s\n", static_cast<long long>(g_launches), name);
 }
 
 void note_copy(const char *name) { g_last_kernel = name; }
@@ -122,6 +153,14 @@ int dpb_set_tuning(const char *key, int64_t value)
     }
     if (key && std::strcmp(key, "fused_elems_per_thread") == 0 && (value == 4 || value == 8)) {
         g_fused_elems.store(value);
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "verbose") == 0 && (value == 0 || value == 1)) {
+        g_verbose.store(static_cast<int>(value));
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "force_generic") == 0 && (value == 0 || value == 1)) {
+        g_force_generic.store(static_cast<int>(value));
         return DPB_OK;
     }
     return set_error(DPB_ERR_VALUE, "unknown tuning key or value out of range: %s",

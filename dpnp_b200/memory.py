@@ -14,6 +14,7 @@ block may be released while kernels that use it are still in flight.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 
 from . import _lib
@@ -94,7 +95,11 @@ def _require_device() -> None:
 def get_default_queue(device: int | None = None) -> StreamQueue:
     """The library-wide queue of `device` (default: the selected device)."""
     if device is None:
-        device = _current_device[0] if _current_device[0] is not None else 0
+        if _current_device[0] is None:
+            # DPNP_B200_DEVICE: ordinal of the device new arrays go to when none is named (the
+            # reference reads its default device from the environment too, dpnp/config.py:32-59)
+            _current_device[0] = int(os.environ.get("DPNP_B200_DEVICE", "0"))
+        device = _current_device[0]
     q = _default_queues.get(device)
     if q is None:
         with _default_lock:

@@ -636,7 +636,15 @@ int dpb_comm_arg_extreme(void *comm, int typenum, int is_max, const void *src, i
 const char *dpb_last_kernel(void);
 int64_t dpb_launch_count(void);
 void dpb_reset_launch_count(void);
-/* Tuning knob: key "ctas_per_sm" etc.; returns DPB_ERR_VALUE for unknown keys. */
+/* Run-time switches; DPB_ERR_VALUE for unknown keys or values out of range.
+ *   "ctas_per_sm" (1..64)              resident blocks per SM assumed when sizing grids
+ *   "fused_elems_per_thread" (4 | 8)   elements per thread of the fused-chain interpreter
+ *   "verbose" (0 | 1)                  log every kernel choice on stderr; initial value from the
+ *                                      environment variable DPNP_B200_VERBOSE
+ *   "force_generic" (0 | 1)            route every elementwise and reduction call to the generic
+ *                                      strided kernels (a debugging aid: results do not change);
+ *                                      initial value from DPNP_B200_FORCE_GENERIC
+ * They stand where the reference reads its environment (dpnp/config.py:32-59). */
 int dpb_set_tuning(const char *key, int64_t value);
 
 #ifdef __cplusplus

@@ -89,3 +89,31 @@ def test_compute_entry_points_fail_loudly_without_a_device():
 
     with pytest.raises(RuntimeError):
         dp.zeros(4)
+
+
+def test_runtime_switches_are_settable_without_a_device():
+    from dpnp_b200 import _lib
+
+    lib = _lib.lib
+    for key in (b"verbose", b"force_generic"):
+        assert lib.dpb_set_tuning(key, 1) == _lib.OK
+        assert lib.dpb_set_tuning(key, 0) == _lib.OK
+        assert lib.dpb_set_tuning(key, 2) == _lib.ERR_VALUE
+    assert lib.dpb_set_tuning(b"no_such_switch", 1) == _lib.ERR_VALUE
+    assert "no_such_switch" in _lib.last_error()
+
+
+def test_the_pybind11_shim_is_built_and_bound_to_the_same_library():
+    from dpnp_b200 import _lib
+
+    assert _lib.native is not None, "dpnp_b200/_tensor_native*.so is missing: run python dpnp_b200/_build.py"
+    assert _lib.native.version() == _lib.lib.dpb_version().decode()
+    core = _lib.native.ArrayCore(4096, _lib.typenum_of("f4"), 7, 0, (3, 5), (5, 1))
+    assert (core.ptr, core.typenum, core.flags, core.device) == (4096, 10, 7, 0)
+    with pytest.raises(ValueError):
+        _lib.native.ArrayCore(0, 10, 7, 0, (3, 5), (1,))
+    # status codes of the library arrive as the exceptions the reference's modules raise
+    a = _lib.native.ArrayCore(0, 10, 7, 0, (4,), (1,))
+    b = _lib.native.ArrayCore(0, 10, 7, 0, (5,), (1,))
+    with pytest.raises((ValueError, RuntimeError)):
+        _lib.native.binary(0, a, a, b, 0)

@@ -8,7 +8,8 @@ import os
 
 import pytest
 
-REFERENCE_ROOT = os.environ.get("DPNP_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("DPNP_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def test_names_used_by_example_bs_exist():

@@ -8,8 +8,9 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-# where a checkout of the reference lies, if there is one on this machine
-REFERENCE_ROOT = os.environ.get("DPNP_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference: DPNP_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("DPNP_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def test_the_reference_example_file_runs_as_it_is(capsys):
