@@ -164,6 +164,7 @@ PROTOTYPES = {
     "dpb_linspace_step": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
     "dpb_linspace_affine": (_i, [_i, _vp, _i64, _vp, _vp, _i, _vp]),
     "dpb_take_one": (_i, [_i, _vp, _i64, _vp, _vp, _vp]),
+    "dpb_probe_fp64_fma": (_i, [_i64, _i, _vp, _i64, _pi64, _vp]),
     "dpb_comm_load": (_i, [C.c_char_p]),
     "dpb_comm_nccl_version": (_i, [C.POINTER(_i)]),
     "dpb_comm_unique_id": (_i, [_vp]),

@@ -52,9 +52,44 @@ __global__ void __launch_bounds__(kBsThreads)
     }
 }
 
+// Measures what the FP64 pipe can issue: every thread runs `iters` rounds of 8 independent
+// fused multiply-adds (explicit fma(): the library is built without contraction).  The sum of
+// the accumulators is stored so that nothing is optimised away.
+__global__ void __launch_bounds__(256) fp64_fma_probe_kernel(int64_t iters, double seed, double *out)
+{
+    double a0 = seed + threadIdx.x, a1 = a0 + 1, a2 = a0 + 2, a3 = a0 + 3, a4 = a0 + 4, a5 = a0 + 5, a6 = a0 + 6,
+           a7 = a0 + 7;
+    const double m = 0.999999, c = 1e-9;
+    for (int64_t i = 0; i < iters; ++i) {
+        a0 = fma(a0, m, c);
+        a1 = fma(a1, m, c);
+        a2 = fma(a2, m, c);
+        a3 = fma(a3, m, c);
+        a4 = fma(a4, m, c);
+        a5 = fma(a5, m, c);
+        a6 = fma(a6, m, c);
+        a7 = fma(a7, m, c);
+    }
+    out[int64_t(blockIdx.x) * blockDim.x + threadIdx.x] = ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
+}
+
 }  // namespace dpb
 
 using namespace dpb;
+
+extern "C" int dpb_probe_fp64_fma(int64_t iters, int blocks_per_sm, double *scratch, int64_t scratch_elems,
+                                  int64_t *fma_count, void *stream)
+{
+    if (iters < 1 || blocks_per_sm < 1 || blocks_per_sm > 8 || !scratch)
+        return set_error(DPB_ERR_VALUE, "dpb_probe_fp64_fma: bad arguments");
+    const int64_t blocks = int64_t(device_props().sm_count) * blocks_per_sm;
+    if (scratch_elems < blocks * 256) return set_error(DPB_ERR_VALUE, "dpb_probe_fp64_fma: scratch of %lld elements needed",
+                                                       static_cast<long long>(blocks * 256));
+    fp64_fma_probe_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(iters, 1.0, scratch);
+    if (fma_count) *fma_count = blocks * 256 * iters * 8;
+    note_kernel("fp64_fma_probe");
+    return check_launch("fp64_fma_probe");
+}
 
 extern "C" int dpb_black_scholes_f64(int64_t n, const double *price, const double *strike,
                                      const double *t, double rate, double vol, double *call,

@@ -588,6 +588,14 @@ int dpb_linspace_affine(int typenum, void *dst, int64_t nelems, const void *star
  * (dpnp/tensor/_usmarray.pyx: __getitem__, _copy_utils.py:_copy_to_numpy). */
 int dpb_take_one(int typenum, const void *src, int64_t nelems, const void *index, void *dst, void *stream);
 
+/* Measurement aid for the FP64-bound fused kernels: launches SMs x blocks_per_sm blocks of 256
+ * threads that each issue iters x 8 independent double-precision fused multiply-adds, and
+ * reports how many were issued in all; timed by the caller with events, it gives the FP64 FMA
+ * rate the device sustains.  `scratch` receives one double per thread.  No counterpart in the
+ * reference. */
+int dpb_probe_fp64_fma(int64_t iters, int blocks_per_sm, double *scratch, int64_t scratch_elems,
+                       int64_t *fma_count, void *stream);
+
 /* ------------------------------------------- multi-GPU: combining partials */
 /* One process per GPU; arrays are sharded along their leading axis.  The reference has no
  * multi-device execution -- an array and every operation on it are tied to one queue
