@@ -131,12 +131,15 @@ class DPNPBinaryFunc(BinaryElementwiseFunc):
             if dtype is not None:
                 raise _fusion.FusionUnsupported("dtype= inside a fused function")
             return _fusion.trace_binary(self.name_, x1, x2, out)
-        for x in (x1, x2):
-            if not (_is_array(x) or _is_scalar(x)):
-                raise TypeError(f"An array must be any of supported type, but got {type(x)}")
-        if not (_is_array(x1) or _is_array(x2)):
-            raise TypeError("Input should be any of supported array type, got two scalars")
-        _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
+        t1, t2 = type(x1), type(x2)
+        if not (t1 is dpnp_array and t2 is dpnp_array):
+            for x in (x1, x2):
+                if not (_is_array(x) or _is_scalar(x)):
+                    raise TypeError(f"An array must be any of supported type, but got {type(x)}")
+            if not (_is_array(x1) or _is_array(x2)):
+                raise TypeError("Input should be any of supported array type, got two scalars")
+        if kwargs or where is not True or subok is not True or (dtype is not None and out is not None):
+            _check_common_kwargs(self.name_, kwargs, where, subok, dtype, out)
         x1_usm, x2_usm = _usm(x1), _usm(x2)
         out = _unpack_out(out)
         if out is not None and not _is_array(out):

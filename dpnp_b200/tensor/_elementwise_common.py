@@ -67,6 +67,20 @@ def _scalar_operand(value, dtype, queue, shape):
     return v
 
 
+def _broadcast_operand(x, shape):
+    """`x` broadcast to `shape` for a kernel call: the stride-0 view is remembered on the array
+    (arrays are immutable in shape except through the `shape` setter, which drops the cache)."""
+    cache = x._bcast_cache
+    if cache is None:
+        cache = x._bcast_cache = {}
+    v = cache.get(shape)
+    if v is None:
+        if len(cache) >= 8:
+            cache.clear()
+        v = cache[shape] = broadcast_to(x, shape)
+    return v
+
+
 def _coerce_usm_type(types):
     """Result USM type: the first of device, shared, host that any input uses."""
     for t in ("device", "shared", "host"):
@@ -215,6 +229,7 @@ class BinaryElementwiseFunc:
         self.acceptance_fn_ = acceptance_fn
         self.weak_type_resolver_ = weak_type_resolver
         self._direct_cache = {}
+        self._promo_cache = {}
 
     def __str__(self):
         return f"<{self.__name__} '{self.name_}'>"
@@ -339,10 +354,34 @@ class BinaryElementwiseFunc:
                     return out
         if order not in ("K", "C", "F", "A"):
             order = "K"
-        exec_q, res_usm_type = self._placement(o1, o2)
-        res_shape, o1_dtype, o2_dtype = self._resolve(o1, o2)
-        buf1_dt, buf2_dt, res_dt = _find_buf_dtype2(o1_dtype, o2_dtype, self.result_type_resolver_fn_,
-                                                    self.acceptance_fn_)
+        if type(o1) is usm_ndarray and type(o2) is usm_ndarray:
+            # two arrays: placement, broadcast shape and promotion without the scalar handling
+            q1, q2 = o1._queue, o2._queue
+            if not (q1 is q2 or (q1.device == q2.device and q1._stream == q2._stream)):
+                raise ExecutionPlacementError(
+                    "Execution placement can not be unambiguously inferred from input arguments.")
+            exec_q = q1
+            res_usm_type = o1._usm_type if o1._usm_type == o2._usm_type else _coerce_usm_type(
+                (o1._usm_type, o2._usm_type))
+            if o1._shape == o2._shape:
+                res_shape = o1._shape
+            else:
+                try:
+                    res_shape = _broadcast_shape_impl([o1._shape, o2._shape])
+                except ValueError:
+                    raise ValueError("operands could not be broadcast together with shapes "
+                                     f"{o1._shape} and {o2._shape}") from None
+            o1_dtype, o2_dtype = o1._dtype, o2._dtype
+            try:
+                buf1_dt, buf2_dt, res_dt = self._promo_cache[(o1_dtype, o2_dtype)]
+            except KeyError:
+                buf1_dt, buf2_dt, res_dt = self._promo_cache[(o1_dtype, o2_dtype)] = _find_buf_dtype2(
+                    o1_dtype, o2_dtype, self.result_type_resolver_fn_, self.acceptance_fn_)
+        else:
+            exec_q, res_usm_type = self._placement(o1, o2)
+            res_shape, o1_dtype, o2_dtype = self._resolve(o1, o2)
+            buf1_dt, buf2_dt, res_dt = _find_buf_dtype2(o1_dtype, o2_dtype, self.result_type_resolver_fn_,
+                                                        self.acceptance_fn_)
         if res_dt is None:
             raise ValueError(
                 f"function '{self.name_}' does not support input types ({o1_dtype}, {o2_dtype}), "
@@ -404,10 +443,10 @@ class BinaryElementwiseFunc:
                 out = _empty_like_pair_orderK(src1, src2, res_dt, res_shape, res_usm_type, exec_q)
             else:
                 out = _empty(res_shape, res_dt, exec_q, order, res_usm_type)
-        if src1.shape != res_shape:
-            src1 = broadcast_to(src1, res_shape)
-        if src2.shape != res_shape:
-            src2 = broadcast_to(src2, res_shape)
+        if src1._shape != res_shape:
+            src1 = _broadcast_operand(src1, res_shape)
+        if src2._shape != res_shape:
+            src2 = _broadcast_operand(src2, res_shape)
         self.binary_fn_(src1, src2, out, sycl_queue=exec_q)
         if orig_out is not None and orig_out is not out:
             ti._copy_usm_ndarray_into_usm_ndarray(out, orig_out, exec_q)

@@ -129,6 +129,7 @@ class usm_ndarray:
     # per-object caches, filled on first use (class-level defaults keep construction cheap)
     _desc_cache = None
     _core_cache = None
+    _bcast_cache = None
     _extent_cache = 0
     _array_namespace = None
     _usm_type = "device"
@@ -308,6 +309,7 @@ class usm_ndarray:
         self._shape, self._strides, self._flags = r._shape, r._strides, r._flags
         self._desc_cache = None
         self._core_cache = None
+        self._bcast_cache = None
         self._extent_cache = 0
 
     @property
