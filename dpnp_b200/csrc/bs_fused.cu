@@ -6,6 +6,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "ew_erf.cuh"
 
 namespace dpb {
 
@@ -18,8 +19,8 @@ DPB_D void bs_one(double P, double S, double T, double mr, double sst, double &c
     const double y = 1.0 / sqrt(z);
     const double w1 = (a - b + c) * y;
     const double w2 = (a - b - c) * y;
-    const double d1 = 0.5 + 0.5 * erf(w1);
-    const double d2 = 0.5 + 0.5 * erf(w2);
+    const double d1 = 0.5 + 0.5 * erf_f64(w1);
+    const double d2 = 0.5 + 0.5 * erf_f64(w2);
     const double Se = exp(b) * S;
     const double r = P * d1 - Se * d2;
     call = r;

@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "ew_complex.cuh"
+#include "ew_erf.cuh"
 
 namespace dpb {
 
@@ -108,13 +109,15 @@ template <class T> struct ReciprocalOp {
 
 // erf: float16 input is promoted to float32
 // (dpnp/backend/extensions/ufunc/elementwise_functions/erf_funcs.cpp:73-85)
+// The function itself is erf_f64 of ew_erf.cuh (error below 1 ulp); float arguments go through
+// it in double precision and are rounded once.
 template <class T> struct ErfOp {
     using R = std::conditional_t<is_half_v<T>, float, std::conditional_t<is_fp_v<T>, T, NoType>>;
     static DPB_D R apply(T x)
     {
-        if constexpr (std::is_same_v<T, double>) return erf(x);
-        else if constexpr (std::is_same_v<T, float>) return erff(x);
-        else return erff(__half2float(x));
+        if constexpr (std::is_same_v<T, double>) return erf_f64(x);
+        else if constexpr (std::is_same_v<T, float>) return static_cast<float>(erf_f64(static_cast<double>(x)));
+        else return static_cast<float>(erf_f64(static_cast<double>(__half2float(x))));
     }
 };
 
