@@ -251,7 +251,7 @@ def timed_steps(ev, fn, steps, flush=None):
     return ev.elapsed_ms(e0, e1)
 
 
-def median_time_ms(ev, fn, reps, warm=3, batch=1):
+def median_time_ms(ev, fn, reps, warm=3, batch=1, prime=False):
     """Median over `reps` samples of the CUDA-event time of one call of fn.  A sample brackets
     `batch` back-to-back calls and is divided by it: with one call per sample the device sits
     idle between the first event and the launch while the host is still inside the call, and
@@ -261,6 +261,10 @@ def median_time_ms(ev, fn, reps, warm=3, batch=1):
     ts = []
     for _ in range(reps):
         e0, e1 = ev.new(), ev.new()
+        if prime:
+            # one call queued ahead of the start event: the device is still busy with it when the
+            # timed calls arrive, so the host time of the first timed call is not charged either
+            fn()
         ev.record(e0)
         for _ in range(batch):
             fn()
@@ -268,6 +272,31 @@ def median_time_ms(ev, fn, reps, warm=3, batch=1):
         ts.append(ev.elapsed_ms(e0, e1) / batch)
     ts.sort()
     return ts[len(ts) // 2]
+
+
+def measure_fp64_peak(lib, check, ev, q):
+    """FP64 fused multiply-adds per second the device sustains (dpb_probe_fp64_fma, best of 5)."""
+    import dpnp_b200 as dp
+
+    scr = dp.empty(1 << 20)
+    cnt = C.c_int64()
+    best = 0.0
+    for _ in range(5):
+        e0, e1 = ev.new(), ev.new()
+        ev.record(e0)
+        check(lib.dpb_probe_fp64_fma(20000, 8, C.c_void_p(scr.get_array()._ptr), scr.size, C.byref(cnt),
+                                     C.c_void_p(q.stream)))
+        ev.record(e1)
+        best = max(best, cnt.value / (ev.elapsed_ms(e0, e1) * 1e-3))
+    return best
+
+
+# FP64 instructions executed per option by the two fused Black-Scholes kernels (thread-level
+# dfma + dmul + dadd counts of one ncu capture on 2^24 options divided by the options; the capture
+# is summarised under profiles/ and named in the JSON line)
+FP64_INSTR_PER_OPTION = {"black_scholes_f64": None, "ew_fused": None}
+FP64_INSTR_SOURCE = ("ncu smsp__sass_thread_inst_executed_op_{dfma,dmul,dadd}_pred_on.sum of `bench.py --profile-case "
+                     "bs_fused` / `bs_fuse` (2^24 options)")
 
 
 def run_gpu_arm(args):
@@ -511,9 +540,19 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
     # fused Black-Scholes (one pass)
     pp, ps, pt = (a.get_array()._ptr for a in (price, strike, tt))
     pc, pq = call.get_array()._ptr, put.get_array()._ptr
+    fp64_peak = measure_fp64_peak(lib, _lib.check, ev, q)
+
+    def fp64_roofline(kernel, ms_):
+        per = FP64_INSTR_PER_OPTION.get(kernel)
+        if not per:
+            return {"fp64_fma_peak_per_s": fp64_peak}
+        rate = per * n / (ms_ * 1e-3)
+        return {"roofline_fp64": {"bound": "fp64 pipe", "achieved": rate, "peak": fp64_peak, "unit": "FP64 instr/s",
+                                  "frac": rate / fp64_peak, "instr_per_option": per, "source": FP64_INSTR_SOURCE}}
+
     ms = median_time_ms(ev, lambda: lib.dpb_black_scholes_f64(n, pp, ps, pt, RATE, VOL, pc, pq, S), 10, batch=4)
     rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms, "black_scholes_f64",
-        "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option")
+        "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option", **fp64_roofline("black_scholes_f64", ms))
 
     # the same chain through the general front-end: traced once, then one interpreted launch
     chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
@@ -521,7 +560,8 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
     if chain.fused_calls == 0:
         raise RuntimeError(f"the Black-Scholes chain was not fused: {chain.last_reason}")
     rec("c2_black_scholes_fuse_decorator_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms,
-        note="dpnp_b200.fuse: the 26-call chain as a register-machine program, one launch")
+        note="dpnp_b200.fuse: the 26-call chain as a register-machine program, one launch",
+        **fp64_roofline("ew_fused", ms))
 
     # C1: add f32 2^24, rotating over 4 buffer sets (768 MiB > L2)
     m = 1 << 24
@@ -539,9 +579,10 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
         i[0] += 1
         lib.dpb_binary_contig(0, 10, 10, 10, m, a.get_array()._ptr, 0, b.get_array()._ptr, 0, o.get_array()._ptr, 0, S)
 
-    ms = median_time_ms(ev, lambda: [c1_api() for _ in range(8)], 10) / 8
-    rec("c1_add_f32_2^24_api", 12 * m * world, ms, note="8 back-to-back dpnp.add calls per sample, rotating buffers")
-    ms = median_time_ms(ev, lambda: [c1_abi() for _ in range(8)], 10) / 8
+    ms = median_time_ms(ev, c1_api, 10, batch=16, prime=True)
+    rec("c1_add_f32_2^24_api", 12 * m * world, ms,
+        note="16 back-to-back dpnp.add calls per sample behind one queued call, rotating buffers")
+    ms = median_time_ms(ev, c1_abi, 10, batch=16, prime=True)
     rec("c1_add_f32_2^24_c_abi", 12 * m * world, ms)
     del sets
 
