@@ -294,7 +294,7 @@ def measure_fp64_peak(lib, check, ev, q):
 # FP64 instructions executed per option by the two fused Black-Scholes kernels (thread-level
 # dfma + dmul + dadd counts of one ncu capture on 2^24 options divided by the options; the capture
 # is summarised under profiles/ and named in the JSON line)
-FP64_INSTR_PER_OPTION = {"black_scholes_f64": None, "ew_fused": None}
+FP64_INSTR_PER_OPTION = {"black_scholes_f64": 120.0, "ew_fused": 123.0}
 FP64_INSTR_SOURCE = ("ncu smsp__sass_thread_inst_executed_op_{dfma,dmul,dadd}_pred_on.sum of `bench.py --profile-case "
                      "bs_fused` / `bs_fuse` (2^24 options)")
 

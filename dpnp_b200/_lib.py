@@ -116,6 +116,7 @@ PROTOTYPES = {
     "dpb_malloc": (_i, [_sz, _vp, _pvp]),
     "dpb_free": (_i, [_vp, _vp]),
     "dpb_pool_trim": (_i, [_sz]),
+    "dpb_debug_redzone_report": (_i, [_pi64, _pi64, _pi64]),
     "dpb_pool_stats": (_i, [C.POINTER(_sz)] * 4),
     "dpb_pool_set_limit": (_i, [_sz]),
     "dpb_host_alloc": (_i, [_sz, _pvp]),

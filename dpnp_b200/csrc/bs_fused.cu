@@ -29,6 +29,9 @@ DPB_D void bs_one(double P, double S, double T, double mr, double sst, double &c
 
 constexpr int kBsThreads = 256;
 
+// VEC doubles per 16-byte access (2, or 1 for unaligned arrays).  One access per thread and array:
+// keeping 2 or 4 accesses in flight per thread was measured slower (more registers, fewer resident
+// warps; the FP64 pipe is already kept busy by the warps of the other resident blocks).
 template <int VEC>
 __global__ void __launch_bounds__(kBsThreads)
     black_scholes_kernel(const double *__restrict__ price, const double *__restrict__ strike,
@@ -36,8 +39,8 @@ __global__ void __launch_bounds__(kBsThreads)
                          double *__restrict__ call, double *__restrict__ put, int64_t n)
 {
     const int64_t nvec = n / VEC;
-    for (int64_t v = int64_t(blockIdx.x) * kBsThreads + threadIdx.x; v < nvec;
-         v += int64_t(gridDim.x) * kBsThreads) {
+    const int64_t stride = int64_t(gridDim.x) * kBsThreads;
+    for (int64_t v = int64_t(blockIdx.x) * kBsThreads + threadIdx.x; v < nvec; v += stride) {
         vec_t<double, VEC> p = load_vec<vec_t<double, VEC>>(price + v * VEC);
         vec_t<double, VEC> s = load_vec<vec_t<double, VEC>>(strike + v * VEC);
         vec_t<double, VEC> tt = load_vec<vec_t<double, VEC>>(t + v * VEC);
@@ -107,13 +110,11 @@ extern "C" int dpb_black_scholes_f64(int64_t n, const double *price, const doubl
     const int64_t cap = int64_t(device_props().sm_count) * tuning_ctas_per_sm();
     if (aligned) {
         const int64_t blocks = std::max<int64_t>(1, std::min(cap, ceil_div(n / 2, kBsThreads)));
-        black_scholes_kernel<2><<<static_cast<int>(blocks), kBsThreads, 0, s>>>(price, strike, t, mr, sst,
-                                                                            call, put, n);
+        black_scholes_kernel<2><<<static_cast<int>(blocks), kBsThreads, 0, s>>>(price, strike, t, mr, sst, call, put, n);
     }
     else {
         const int64_t blocks = std::max<int64_t>(1, std::min(cap, ceil_div(n, kBsThreads)));
-        black_scholes_kernel<1><<<static_cast<int>(blocks), kBsThreads, 0, s>>>(price, strike, t, mr, sst,
-                                                                            call, put, n);
+        black_scholes_kernel<1><<<static_cast<int>(blocks), kBsThreads, 0, s>>>(price, strike, t, mr, sst, call, put, n);
     }
     note_kernel("black_scholes_f64");
     return check_launch("black_scholes_f64");

@@ -105,6 +105,62 @@ static std::atomic<int64_t> g_fused_elems{8};
 int64_t tuning_fused_elems() { return g_fused_elems.load(std::memory_order_relaxed); }
 
 
+// --------------------------------------------------------- guarded blocks
+// A debugging aid for kernels that write where they should not (compute-sanitizer's memcheck is
+// not always available): when switched on ("redzones" tuning key, DPNP_B200_REDZONES=1), every
+// block of the pool gets kRedzone bytes in front and behind, filled with a pattern when the block
+// is handed out and compared with it when the block comes back.  Both steps are kernels on the
+// block's stream; a mismatch is counted in device memory and the first one is remembered.  Nothing
+// traps: dpb_debug_redzone_report reads the counters.
+constexpr size_t kRedzone = 512;
+constexpr unsigned char kRedzoneByte = 0xA5;
+__device__ unsigned long long g_rz_bad_bytes = 0;
+__device__ unsigned long long g_rz_bad_blocks = 0;
+__device__ unsigned long long g_rz_first[3] = {0, 0, 0};   // user pointer, user size, offset of the bad byte
+
+__global__ void redzone_fill_kernel(unsigned char *base, size_t user_bytes)
+{
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < kRedzone) {
+        base[i] = kRedzoneByte;
+        base[kRedzone + user_bytes + i] = kRedzoneByte;
+    }
+}
+
+__global__ void redzone_check_kernel(const unsigned char *base, size_t user_bytes)
+{
+    __shared__ unsigned bad;
+    if (threadIdx.x == 0) bad = 0;
+    __syncthreads();
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < 2 * kRedzone) {
+        const bool front = i < kRedzone;
+        const size_t at = front ? i : user_bytes + i;   // offset from base
+        if (base[at] != kRedzoneByte) {
+            atomicAdd(&bad, 1u);
+            if (atomicAdd(&g_rz_bad_bytes, 1ull) == 0) {
+                g_rz_first[0] = reinterpret_cast<unsigned long long>(base + kRedzone);
+                g_rz_first[1] = user_bytes;
+                // bytes before the block count as negative offsets
+                g_rz_first[2] = static_cast<unsigned long long>(static_cast<long long>(at) - static_cast<long long>(kRedzone));
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && bad) atomicAdd(&g_rz_bad_blocks, 1ull);
+}
+
+static std::atomic<int> g_redzones{-1};
+static bool redzones_on()
+{
+    int v = g_redzones.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = env_flag("DPNP_B200_REDZONES");
+        g_redzones.store(v);
+    }
+    return v != 0;
+}
+
 // ------------------------------------------------------------------- pool
 struct PoolState {
     std::atomic<bool> configured{false};
@@ -115,7 +171,13 @@ static PoolState g_pool[kMaxDevices];
 static std::atomic<size_t> g_pool_limit{0};
 static std::mutex g_pool_mutex;
 // size of every live block, so that dpb_free can keep the live-byte count exact
-static std::unordered_map<void *, std::pair<int, size_t>> g_blocks;
+struct BlockInfo {
+    int device;
+    size_t request;   // bytes taken from the pool (with the guard zones, if any)
+    size_t user;      // bytes the caller asked for
+    bool guarded;
+};
+static std::unordered_map<void *, BlockInfo> g_blocks;
 static std::mutex g_blocks_mutex;
 
 static int configure_pool(int dev)
@@ -153,6 +215,10 @@ int dpb_set_tuning(const char *key, int64_t value)
     }
     if (key && std::strcmp(key, "fused_elems_per_thread") == 0 && (value == 4 || value == 8)) {
         g_fused_elems.store(value);
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "redzones") == 0 && (value == 0 || value == 1)) {
+        g_redzones.store(static_cast<int>(value));
         return DPB_OK;
     }
     if (key && std::strcmp(key, "verbose") == 0 && (value == 0 || value == 1)) {
@@ -269,7 +335,9 @@ int dpb_malloc(size_t nbytes, void *stream, void **ptr)
 {
     if (!ptr) return set_error(DPB_ERR_VALUE, "dpb_malloc: null result pointer");
     *ptr = nullptr;
-    size_t request = nbytes ? nbytes : 1;
+    const bool guarded = redzones_on();
+    const size_t user = nbytes ? nbytes : 1;
+    size_t request = guarded ? ((user + 15) / 16 * 16 + 2 * kRedzone) : user;
     size_t limit = g_pool_limit.load(std::memory_order_relaxed);
     if (limit && request > limit) {
         // decided before any CUDA call, so the check also works without a device
@@ -299,9 +367,15 @@ int dpb_malloc(size_t nbytes, void *stream, void **ptr)
     size_t high = g_pool[dev].live_high.load();
     while (now > high && !g_pool[dev].live_high.compare_exchange_weak(high, now)) {
     }
+    if (guarded) {
+        // the trailing zone starts right after the user's bytes, so a write one element past the end is seen
+        redzone_fill_kernel<<<(kRedzone + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<unsigned char *>(p), user);
+        p = static_cast<unsigned char *>(p) + kRedzone;
+    }
     {
         std::lock_guard<std::mutex> lock(g_blocks_mutex);
-        g_blocks[p] = {dev, request};
+        g_blocks[p] = BlockInfo{dev, request, user, guarded};
     }
     *ptr = p;
     return DPB_OK;
@@ -310,15 +384,40 @@ int dpb_malloc(size_t nbytes, void *stream, void **ptr)
 int dpb_free(void *ptr, void *stream)
 {
     if (!ptr) return DPB_OK;
+    BlockInfo info;
     {
         std::lock_guard<std::mutex> lock(g_blocks_mutex);
         auto it = g_blocks.find(ptr);
         if (it == g_blocks.end())
             return set_error(DPB_ERR_VALUE, "dpb_free: %p was not returned by dpb_malloc", ptr);
-        g_pool[it->second.first].live.fetch_sub(it->second.second);
+        info = it->second;
+        g_pool[info.device].live.fetch_sub(info.request);
         g_blocks.erase(it);
     }
+    if (info.guarded) {
+        unsigned char *base = static_cast<unsigned char *>(ptr) - kRedzone;
+        redzone_check_kernel<<<(2 * kRedzone + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(base, info.user);
+        ptr = base;
+    }
     DPB_CUDA_TRY(cudaFreeAsync(ptr, static_cast<cudaStream_t>(stream)));
+    return DPB_OK;
+}
+
+int dpb_debug_redzone_report(int64_t *bad_blocks, int64_t *bad_bytes, int64_t *first3)
+{
+    DPB_CUDA_TRY(cudaDeviceSynchronize());
+    unsigned long long blocks = 0, bytes = 0, first[3] = {0, 0, 0};
+    DPB_CUDA_TRY(cudaMemcpyFromSymbol(&blocks, g_rz_bad_blocks, sizeof(blocks)));
+    DPB_CUDA_TRY(cudaMemcpyFromSymbol(&bytes, g_rz_bad_bytes, sizeof(bytes)));
+    DPB_CUDA_TRY(cudaMemcpyFromSymbol(first, g_rz_first, sizeof(first)));
+    if (bad_blocks) *bad_blocks = static_cast<int64_t>(blocks);
+    if (bad_bytes) *bad_bytes = static_cast<int64_t>(bytes);
+    if (first3)
+        for (int i = 0; i < 3; ++i) first3[i] = static_cast<int64_t>(first[i]);
+    const unsigned long long zero[3] = {0, 0, 0};
+    DPB_CUDA_TRY(cudaMemcpyToSymbol(g_rz_bad_blocks, zero, sizeof(unsigned long long)));
+    DPB_CUDA_TRY(cudaMemcpyToSymbol(g_rz_bad_bytes, zero, sizeof(unsigned long long)));
+    DPB_CUDA_TRY(cudaMemcpyToSymbol(g_rz_first, zero, sizeof(zero)));
     return DPB_OK;
 }
 

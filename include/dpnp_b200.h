@@ -254,6 +254,15 @@ int dpb_malloc(size_t nbytes, void *stream, void **ptr);
 int dpb_free(void *ptr, void *stream);
 /* Release cached memory back to the driver down to `keep_bytes`. */
 int dpb_pool_trim(size_t keep_bytes);
+/* Guarded blocks, a debugging aid in place of a memory checker: with the "redzones" switch on
+ * (dpb_set_tuning, or DPNP_B200_REDZONES=1 in the environment) every block handed out by
+ * dpb_malloc carries 512 patterned bytes in front and behind, compared with the pattern when the
+ * block is freed (both by small kernels on the block's stream; nothing traps).  This call waits
+ * for the device, reports how many freed blocks / bytes were found overwritten since the last
+ * report, and for the first of them {user pointer, user size, offset of the byte relative to the
+ * block's start}, then clears the counters.  Writes that land farther than 512 bytes from a block
+ * are not seen.  No counterpart in the reference. */
+int dpb_debug_redzone_report(int64_t *bad_blocks, int64_t *bad_bytes, int64_t *first3);
 /* Pool counters of the current device: bytes reserved from the driver and
  * bytes handed out, now and at the high-water mark. */
 int dpb_pool_stats(size_t *reserved, size_t *used, size_t *reserved_high, size_t *used_high);
@@ -649,6 +658,8 @@ void dpb_reset_launch_count(void);
  *   "fused_elems_per_thread" (4 | 8)   elements per thread of the fused-chain interpreter
  *   "verbose" (0 | 1)                  log every kernel choice on stderr; initial value from the
  *                                      environment variable DPNP_B200_VERBOSE
+ *   "redzones" (0 | 1)                 guarded pool blocks, see dpb_debug_redzone_report; initial value
+ *                                      from DPNP_B200_REDZONES
  *   "force_generic" (0 | 1)            route every elementwise and reduction call to the generic
  *                                      strided kernels (a debugging aid: results do not change);
  *                                      initial value from DPNP_B200_FORCE_GENERIC
