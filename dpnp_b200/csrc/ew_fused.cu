@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "ew_ops.cuh"
+#include "ew_erf.cuh"
 
 namespace dpb {
 

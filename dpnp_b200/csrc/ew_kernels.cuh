@@ -61,6 +61,11 @@ template <class F> constexpr int ew_vec_width()
     else return vec_width<typename F::In0, typename F::In1, typename F::In2, typename F::Out>();
 }
 
+// 16-byte accesses per thread of the contiguous kernel for one streamed input: 8 unless the
+// functor names its own (kUnroll)
+template <class F, class = void> struct ew_unroll { static constexpr int value = 8; };
+template <class F> struct ew_unroll<F, std::void_t<decltype(F::kUnroll)>> { static constexpr int value = F::kUnroll; };
+
 // ------------------------------------------------------------- contiguous
 // Tile = 256 threads x VEC elements x UNROLL vectors, one tile per block (the
 // kernel keeps a stride loop so a capped grid still covers any size); the ragged
@@ -717,7 +722,7 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         if (aligned) {
             if constexpr (NIN == 0) DPB_CONTIG_LAUNCH(8, 0u)
             if constexpr (NIN == 1) {
-                if (m == 0) DPB_CONTIG_LAUNCH(8, 0u)
+                if (m == 0) DPB_CONTIG_LAUNCH(ew_unroll<F>::value, 0u)
             }
             if constexpr (NIN == 2) {
                 if (m == 0) DPB_CONTIG_LAUNCH(4, 0u)

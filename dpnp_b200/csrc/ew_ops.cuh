@@ -10,9 +10,12 @@
 
 #include "common.cuh"
 #include "ew_complex.cuh"
-#include "ew_erf.cuh"
 
 namespace dpb {
+
+// defined in ew_erf.cuh, which the translation units that instantiate ErfOp include (its table
+// and its long body stay out of all the others)
+DPB_HD double erf_f64(double x);
 
 struct NoType {};
 
@@ -115,6 +118,9 @@ template <class T> struct ReciprocalOp {
 // The function itself is erf_f64 of ew_erf.cuh (error below 1 ulp); float arguments go through
 // it in double precision and are rounded once.
 template <class T> struct ErfOp {
+    // every call gathers from a table: fewer elements per thread keep more warps resident to
+    // hide the lookups
+    static constexpr int kUnroll = 4;
     using R = std::conditional_t<is_half_v<T>, float, std::conditional_t<is_fp_v<T>, T, NoType>>;
     static DPB_D R apply(T x)
     {

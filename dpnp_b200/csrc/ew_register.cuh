@@ -53,8 +53,13 @@ int ew_entry(const EwPlan &plan, const void *const *in, void *out, cudaStream_t 
     return launch_ew(F(), plan, in, out, stream);
 }
 
+// 16-byte accesses per thread of the contiguous kernel: an operator may ask for fewer (kUnroll)
+template <class O, class = void> struct op_unroll { static constexpr int value = 8; };
+template <class O> struct op_unroll<O, std::void_t<decltype(O::kUnroll)>> { static constexpr int value = O::kUnroll; };
+
 template <template <class> class Op, class T> struct UnaryF {
     static constexpr int NIN = 1;
+    static constexpr int kUnroll = op_unroll<Op<T>>::value;
     using In0 = T;
     using In1 = char;
     using In2 = char;

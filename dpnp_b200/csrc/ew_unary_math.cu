@@ -1,5 +1,6 @@
 // Unary transcendental operations.
 #include "ew_register.cuh"
+#include "ew_erf.cuh"
 namespace dpb {
 void register_unary_math(EwTables &t)
 {
