@@ -294,9 +294,9 @@ def measure_fp64_peak(lib, check, ev, q):
 # FP64 instructions executed per option by the two fused Black-Scholes kernels (thread-level
 # dfma + dmul + dadd counts of one ncu capture on 2^24 options divided by the options; the capture
 # is summarised under profiles/ and named in the JSON line)
-FP64_INSTR_PER_OPTION = {"black_scholes_f64": 127.2, "ew_fused": 130.2}
+FP64_INSTR_PER_OPTION = {"black_scholes_f64": 127.2, "ew_fused": 130.2, "ew_fused_specialized": 130.2}
 FP64_INSTR_SOURCE = ("ncu smsp__sass_thread_inst_executed_op_{dfma,dmul,dadd}_pred_on.sum of `bench.py --profile-case "
-                     "bs_fused` / `bs_fuse` (2^24 options)")
+                     "bs_fused` / `bs_fuse` / `bs_fuse_interpreted` (2^24 options)")
 
 
 def run_gpu_arm(args):
@@ -554,14 +554,20 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
     rec("c2_black_scholes_fused_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms, "black_scholes_f64",
         "fp64-pipe bound: 2 erf + log + exp + sqrt + 2 div per option", **fp64_roofline("black_scholes_f64", ms))
 
-    # the same chain through the general front-end: traced once, then one interpreted launch
-    chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
-    ms = median_time_ms(ev, lambda: chain(price, strike, tt, call, put), 10, batch=4)
-    if chain.fused_calls == 0:
-        raise RuntimeError(f"the Black-Scholes chain was not fused: {chain.last_reason}")
-    rec("c2_black_scholes_fuse_decorator_f64_2^26", n * BYTES_PER_OPTION_FUSED * world, ms,
-        note="dpnp_b200.fuse: the 26-call chain as a register-machine program, one launch",
-        **fp64_roofline("ew_fused", ms))
+    # the same chain through the general front-end, traced once: as the kernel compiled for it at
+    # the first call (the default where NVRTC is found), and interpreted
+    for mode, label, kern in (("auto", "c2_black_scholes_fuse_decorator_f64_2^26", "ew_fused_specialized"),
+                              ("interpret", "c2_black_scholes_fuse_interpreted_f64_2^26", "ew_fused")):
+        chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_), mode=mode)
+        ms = median_time_ms(ev, lambda: chain(price, strike, tt, call, put), 10, batch=4)
+        if chain.fused_calls == 0:
+            raise RuntimeError(f"the Black-Scholes chain was not fused: {chain.last_reason}")
+        if chain.last_executor == "interpreted":
+            kern = "ew_fused"
+        rec(label, n * BYTES_PER_OPTION_FUSED * world, ms,
+            note=f"dpnp_b200.fuse(mode={mode!r}): the 26-call chain traced into one program, one launch, "
+                 f"executor: {chain.last_executor}",
+            **fp64_roofline(kern, ms))
 
     # C1: add f32 2^24, rotating over 4 buffer sets (768 MiB > L2)
     m = 1 << 24
@@ -808,7 +814,7 @@ def bind_to_gpu_cores(local_rank, world):
         return None
 
 
-PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "fuse_cheap", "cumsum_axis1", "cumsum_flat", "generic_stride2", "rows_bcast",
+PROFILE_CASES = ("ew_add_f32", "ew_mul_f64", "ew_mul_scalar_f64", "ew_erf_f64", "bs_fused", "bs_fuse", "bs_fuse_interpreted", "fuse_cheap", "cumsum_axis1", "cumsum_flat", "generic_stride2", "rows_bcast",
                  "argmax_axis0", "sum_axis1",
                  "sum_axis0", "mean_all", "transpose_c4", "max_i32", "argmax_i32")
 
@@ -837,11 +843,12 @@ def profile_case(name, launches=3):
         S = C.c_void_p(q.stream)
         fn = lambda: _lib.lib.dpb_black_scholes_f64(n, p.get_array()._ptr, s.get_array()._ptr, t.get_array()._ptr,
                                                     RATE, VOL, c.get_array()._ptr, u.get_array()._ptr, S)
-    elif name == "bs_fuse":
+    elif name in ("bs_fuse", "bs_fuse_interpreted"):
         n = 1 << 24
         p, s, t = dp.random.uniform(10, 50, n), dp.random.uniform(10, 50, n), dp.random.uniform(1, 2, n)
         c, u = dp.empty(n), dp.empty(n)
-        chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_))
+        chain = dp.fuse(lambda p_, s_, t_, c_, q_: black_scholes(dp, p_, s_, t_, RATE, VOL, c_, q_),
+                        mode="interpret" if name == "bs_fuse_interpreted" else "compile")
         fn = lambda: chain(p, s, t, c, u)
     elif name == "fuse_cheap":
         # 60 dependent multiply/add instructions with immediate operands: almost no arithmetic, so

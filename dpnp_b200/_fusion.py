@@ -7,13 +7,20 @@ kernel per call, and a Python scalar operand becomes a stride-0 array
 (dpnp/tensor/_elementwise_common.py:655-659).  A function wrapped in :func:`fuse` is
 instead *traced*: its array arguments are replaced by :class:`FusedValue` stand-ins, every
 operator and ufunc applied to them records a node of an expression graph, and the graph is
-compiled once into a register-machine program that ``dpb_fused_elementwise`` interprets on
-the device -- the chain's inputs are read once and its results written once.
+compiled once into a register-machine program -- the chain's inputs are read once and its
+results written once.  The program has two executors behind the C ABI:
 
-The interpreter applies the same device operators as the per-op kernels, in the same order,
-with scalars converted to the array type exactly as the per-op path converts them, so the
-result has the bits of the unfused chain.  Common subexpressions are evaluated once, which
-does not change any value.
+* ``dpb_fused_elementwise_specialized`` writes it out as straight-line CUDA C++ over the operator
+  classes of the per-op kernels, compiles that with NVRTC at the first call and keeps the kernel:
+  the chain then runs like a kernel written by hand for it (mode ``"compile"``);
+* ``dpb_fused_elementwise`` interprets it on the device, with no compiler involved (mode
+  ``"interpret"``; about twice the time on an arithmetic-heavy chain).
+
+``"auto"`` (the default; ``DPNP_B200_FUSE`` overrides it) compiles when NVRTC, the driver library
+and the headers are found and interprets otherwise.  Both executors apply the same device
+operators as the per-op kernels, in the same order, with scalars converted to the array type
+exactly as the per-op path converts them, so the result has the bits of the unfused chain.
+Common subexpressions are evaluated once, which does not change any value.
 
 What is fused: float32 / float64 C-contiguous arrays of one common shape (size-1 arrays are
 broadcast), Python ``int`` / ``float`` scalars, arithmetic, comparisons feeding ``where`` or
@@ -28,6 +35,7 @@ from __future__ import annotations
 
 import ctypes as C
 import functools
+import os
 import struct
 
 import numpy as np
@@ -71,6 +79,29 @@ class dpb_fused_program(C.Structure):
 
 _lib.lib.dpb_fused_elementwise.restype = C.c_int
 _lib.lib.dpb_fused_elementwise.argtypes = [C.POINTER(dpb_fused_program), C.c_int64, C.c_void_p]
+_lib.lib.dpb_fused_elementwise_specialized.restype = C.c_int
+_lib.lib.dpb_fused_elementwise_specialized.argtypes = [C.POINTER(dpb_fused_program), C.c_int64, C.c_void_p]
+_lib.lib.dpb_fused_specialized_source.argtypes = [C.POINTER(dpb_fused_program), C.c_char_p, C.c_int64,
+                                                  C.POINTER(C.c_int64)]
+_lib.lib.dpb_fused_specialize_compile.argtypes = [C.POINTER(dpb_fused_program), C.POINTER(C.c_int64)]
+
+MODES = ("auto", "compile", "interpret")
+_specialize_available = None
+
+
+def specialize_available():
+    """Whether chains can be compiled at run time here (NVRTC, the driver library, the headers)."""
+    global _specialize_available
+    if _specialize_available is None:
+        _specialize_available = bool(_lib.lib.dpb_fused_specialize_available())
+    return _specialize_available
+
+
+def default_mode():
+    mode = os.environ.get("DPNP_B200_FUSE", "auto").strip().lower() or "auto"
+    if mode not in MODES:
+        raise ValueError(f"DPNP_B200_FUSE={mode!r}: expected one of {MODES}")
+    return mode
 
 
 # --------------------------------------------------------------------------- tracing
@@ -456,11 +487,39 @@ class _Program:
                 len(self.out_bind) > _MAX_OUT or n_reg > min(_MAX_REG, _OPND_IMM) or
                 len(imms) > _OPND_IN - _OPND_IMM):
             raise FusionUnsupported("chain exceeds the limits of the interpreter")
+        self.specialize_failed = None          # why run-time compilation of this program failed, if it did
         self.n_reg = n_reg
         self.n_instr = len(code)
         self.code = (C.c_uint64 * max(1, len(code)))(*code)
         self.imm = (C.c_double * max(1, len(imms)))(*imms)
         self.n_imm = len(imms)
+
+    def _descriptor(self, ins=None, flags=None, outs=None):
+        """The C descriptor; without arrays (source(), compile()) the pointers are placeholders."""
+        n_in, n_out = len(self.in_slots), len(self.out_bind)
+        if ins is None:
+            ins = (C.c_void_p * max(1, n_in))(*[16] * n_in)
+            outs = (C.c_void_p * max(1, n_out))(*[16] * n_out)
+            scalar = getattr(self, "scalar_slots", None)
+            flags = (C.c_int32 * max(1, n_in))(*[int(scalar[s]) if scalar else 0 for s in self.in_slots])
+        desc = dpb_fused_program(_lib.typenum_of(self.dtype), self.n_instr, self.n_reg, self.n_imm, n_in, n_out,
+                                 self.code, self.imm, ins, flags, outs)
+        desc._keep = (ins, flags, outs)
+        return desc
+
+    def source(self):
+        """The CUDA C++ that mode "compile" builds for this program (no device involved)."""
+        desc, need = self._descriptor(), C.c_int64(0)
+        _lib.check(_lib.lib.dpb_fused_specialized_source(C.byref(desc), None, 0, C.byref(need)))
+        buf = C.create_string_buffer(need.value)
+        _lib.check(_lib.lib.dpb_fused_specialized_source(C.byref(desc), buf, need.value, None))
+        return buf.value.decode()
+
+    def compile(self):
+        """Compile the program now (no device needed); returns the size of the device code."""
+        desc, size = self._descriptor(), C.c_int64(0)
+        _lib.check(_lib.lib.dpb_fused_specialize_compile(C.byref(desc), C.byref(size)))
+        return size.value
 
     def listing(self):
         """Human-readable instruction list (for tests and debugging)."""
@@ -501,9 +560,13 @@ def _full_arrays(arrays):
 
 
 class _Fused:
-    def __init__(self, func):
+    def __init__(self, func, mode=None):
         functools.update_wrapper(self, func)
         self._func = func
+        if mode is not None and mode not in MODES:
+            raise ValueError(f"fuse(mode={mode!r}): expected one of {MODES}")
+        self.mode = mode                   # None: default_mode() at every call
+        self.last_executor = None          # "specialized" or "interpreted"
         self._cache = {}
         self.fused_calls = 0
         self.eager_calls = 0
@@ -653,10 +716,22 @@ class _Fused:
                 new[i] = dpt.empty(first_full.shape, dtype=prog.dtype, sycl_queue=q)
                 outs.append(new[i]._ptr)
         outp = (C.c_void_p * max(1, len(outs)))(*outs)
-        desc = dpb_fused_program(
-            _lib.typenum_of(prog.dtype), prog.n_instr, prog.n_reg, prog.n_imm, len(prog.in_slots), len(outs),
-            prog.code, prog.imm, ins, flags, outp)
-        _lib.check(_lib.lib.dpb_fused_elementwise(C.byref(desc), n, C.c_void_p(q.stream)))
+        desc = prog._descriptor(ins, flags, outp)
+        mode = self.mode or default_mode()
+        stream = C.c_void_p(q.stream)
+        specialized = mode == "compile" or (mode == "auto" and specialize_available()
+                                            and prog.specialize_failed is None)
+        if specialized:
+            status = _lib.lib.dpb_fused_elementwise_specialized(C.byref(desc), n, stream)
+            if status == _lib.ERR_RUNTIME and mode == "auto":
+                # the compiler is there but this chain did not build: remember why, interpret it
+                prog.specialize_failed = _lib.last_error()
+                specialized = False
+            else:
+                _lib.check(status)
+        if not specialized:
+            _lib.check(_lib.lib.dpb_fused_elementwise(C.byref(desc), n, stream))
+        self.last_executor = "specialized" if specialized else "interpreted"
 
         def build(t):
             kind = t[0]
@@ -684,10 +759,13 @@ class _Fused:
 def fuse(func=None, /, **options):
     """Decorator: evaluate the elementwise chain in ``func`` with one kernel launch.
 
-    ``@fuse`` and ``@fuse()`` are both accepted.  The wrapped callable has the attributes
-    ``fused_calls`` / ``eager_calls`` / ``last_reason`` (why the last call was not fused)."""
+    ``@fuse`` and ``@fuse()`` are both accepted; ``mode`` is "auto" (default), "compile" or
+    "interpret" (see the module docstring).  The wrapped callable has the attributes
+    ``fused_calls`` / ``eager_calls`` / ``last_reason`` (why the last call was not fused) and
+    ``last_executor`` ("specialized" or "interpreted")."""
+    mode = options.pop("mode", None)
     if options:
         raise TypeError(f"fuse() got unexpected options {sorted(options)}")
     if func is None:
-        return _Fused
-    return _Fused(func)
+        return lambda f: _Fused(f, mode)
+    return _Fused(func, mode)

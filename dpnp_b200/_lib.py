@@ -158,6 +158,11 @@ PROTOTYPES = {
     "dpb_search_over_axis": (_i, [_i, _parr, _i, _parr, _vp]),
     "dpb_black_scholes_f64": (_i, [_i64, _vp, _vp, _vp, _dbl, _dbl, _vp, _vp, _vp]),
     "dpb_fused_elementwise": (_i, [_vp, _i64, _vp]),
+    "dpb_fused_elementwise_specialized": (_i, [_vp, _i64, _vp]),
+    "dpb_fused_specialize_available": (_i, []),
+    "dpb_fused_set_include_path": (_i, [C.c_char_p]),
+    "dpb_fused_specialized_source": (_i, [_vp, C.c_char_p, _i64, _pi64]),
+    "dpb_fused_specialize_compile": (_i, [_vp, _pi64]),
     "dpb_accumulate_over_axis": (_i, [_i, _parr, _parr, _i, _vp]),
     "dpb_accumulate_dtype_supported": (_i, [_i, _i, _i]),
     "dpb_random_uniform": (_i, [_i, _vp, _i64, _dbl, _dbl, _u64, _u64, _vp]),

@@ -209,7 +209,7 @@ struct FastDiv32 {
     uint32_t mul;
     uint32_t shift;
     FastDiv32() = default;
-    __host__ explicit FastDiv32(uint32_t divisor) : d(divisor)
+    explicit FastDiv32(uint32_t divisor) : d(divisor)   // host side (no attribute: the run-time compiler rejects __host__)
     {
         uint32_t s = 0;
         while ((uint64_t(1) << s) < divisor) ++s;

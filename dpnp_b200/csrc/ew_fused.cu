@@ -20,21 +20,12 @@
 #include "common.cuh"
 #include "ew_ops.cuh"
 #include "ew_erf.cuh"
+#include "ew_fused.h"
 
 namespace dpb {
 
 constexpr int kFusedThreads = 128;
-constexpr int kFusedMaxInstr = 192;
-constexpr int kFusedMaxImm = 48;
-constexpr int kFusedMaxIn = 12;
-constexpr int kFusedMaxOut = 8;
-constexpr int kFusedMaxReg = 24;
 
-// operand encoding (8 bits)
-constexpr unsigned kOpndImm = 64;      // 64 + i: immediate i
-constexpr unsigned kOpndIn = 128;      // 128 + i: input array i, read where it is used
-constexpr unsigned kOpndAcc = 255;     // result of the previous instruction
-constexpr unsigned kNoDst = 255;       // result stays in the accumulator only
 
 // The host turns every instruction word into one or two micro-operations whose fields the
 // kernel can use as they are (operand kind resolved, shared-memory offsets multiplied out,
@@ -337,7 +328,9 @@ bool operand_ok(unsigned x, int n_reg, int n_imm, int n_in, bool first)
 
 using namespace dpb;
 
-extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, void *stream)
+// Everything a launch relies on is checked here, once, on the host: the limits, the pointers and
+// every index of every instruction.  `aligned`: all array pointers allow 16-byte accesses.
+int dpb::fused_check_program(const dpb_fused_program *prog, int64_t n, bool *aligned_out)
 {
     if (!prog) return set_error(DPB_ERR_VALUE, "fused program is null");
     if (prog->typenum != DPB_FLOAT && prog->typenum != DPB_DOUBLE)
@@ -348,23 +341,16 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
         return set_error(DPB_ERR_VALUE, "fused program exceeds the limits of the interpreter "
                                         "(192 instructions, 48 immediates, 12 inputs, 8 outputs, 24 registers)");
     if (n < 0) return set_error(DPB_ERR_VALUE, "negative element count");
-    FusedParams prm;
-    std::memset(&prm, 0, sizeof(prm));
     bool aligned = true;
     for (int i = 0; i < prog->n_in; ++i) {
         if (!prog->in[i]) return set_error(DPB_ERR_VALUE, "fused program: null input pointer");
-        prm.in[i] = prog->in[i];
-        prm.in_scalar[i] = prog->in_is_scalar ? prog->in_is_scalar[i] : 0;
-        if (!prm.in_scalar[i]) aligned = aligned && is_aligned(prog->in[i], 16);
+        const bool scalar = prog->in_is_scalar && prog->in_is_scalar[i];
+        if (!scalar) aligned = aligned && is_aligned(prog->in[i], 16);
     }
     for (int i = 0; i < prog->n_out; ++i) {
         if (!prog->out[i]) return set_error(DPB_ERR_VALUE, "fused program: null output pointer");
-        prm.out[i] = prog->out[i];
         aligned = aligned && is_aligned(prog->out[i], 16);
     }
-    prm.vector_io = aligned ? 1 : 0;
-    for (int i = 0; i < prog->n_imm; ++i) prm.imm[i] = prog->imm[i];
-    // every index the kernel will use is checked here, once, on the host
     for (int pc = 0; pc < prog->n_instr; ++pc) {
         const uint64_t w = prog->code[pc];
         const int op = static_cast<int>(w & 0xff);
@@ -386,6 +372,23 @@ extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, v
         if (ok && op != DPB_FUSED_STORE) ok = dst == kNoDst || static_cast<int>(dst) < prog->n_reg;
         if (!ok) return set_error(DPB_ERR_VALUE, "fused program: malformed instruction");
     }
+    if (aligned_out) *aligned_out = aligned;
+    return DPB_OK;
+}
+
+extern "C" int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, void *stream)
+{
+    bool aligned = true;
+    DPB_TRY(fused_check_program(prog, n, &aligned));
+    FusedParams prm;
+    std::memset(&prm, 0, sizeof(prm));
+    for (int i = 0; i < prog->n_in; ++i) {
+        prm.in[i] = prog->in[i];
+        prm.in_scalar[i] = prog->in_is_scalar ? prog->in_is_scalar[i] : 0;
+    }
+    for (int i = 0; i < prog->n_out; ++i) prm.out[i] = prog->out[i];
+    prm.vector_io = aligned ? 1 : 0;
+    for (int i = 0; i < prog->n_imm; ++i) prm.imm[i] = prog->imm[i];
     if (n == 0 || prog->n_instr == 0) return DPB_OK;
     const size_t elem = prog->typenum == DPB_DOUBLE ? 8 : 4;
     const int K = static_cast<int>(tuning_fused_elems());

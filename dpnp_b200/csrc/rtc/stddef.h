@@ -1,0 +1,3 @@
+// Stand-in for <stddef.h> when a fused chain is compiled at run time: the run-time compiler has the
+// declarations built in and no host headers.
+#pragma once

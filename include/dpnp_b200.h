@@ -566,6 +566,30 @@ typedef struct dpb_fused_program {
  * program (every index is checked on the host before the launch). */
 int dpb_fused_elementwise(const dpb_fused_program *prog, int64_t n, void *stream);
 
+/* The same program as a kernel of its own: written out as straight-line CUDA C++ over the operator
+ * classes of the per-op kernels (one statement per instruction, registers as local variables),
+ * compiled with NVRTC at first use for the current device and kept for the life of the process
+ * (keyed by type, instruction words and which inputs are single elements; the immediates and the
+ * pointers are arguments of the kernel).  Same results, bit for bit, as dpb_fused_elementwise and
+ * as the unfused chain.  NVRTC and the driver library are loaded with dlopen at first use;
+ * DPB_ERR_RUNTIME (with the compiler's log in dpb_last_error) if they are missing or the
+ * compilation fails.  No counterpart in the reference, which has no fusion. */
+int dpb_fused_elementwise_specialized(const dpb_fused_program *prog, int64_t n, void *stream);
+/* 1 if NVRTC, the driver library, the operator headers (directory csrc next to this library) and
+ * the CUDA headers are all found, else 0. */
+int dpb_fused_specialize_available(void);
+/* Directories searched for headers by the run-time compilation, separated by ':' (the operator
+ * headers, the stand-ins of csrc/rtc, the CUDA toolkit's include directory).  NULL or "" restores
+ * the default: csrc/rtc and csrc next to this library, then $DPNP_B200_CUDA_INCLUDE,
+ * $CUDA_HOME/include, $CUDA_PATH/include or /usr/local/cuda/include. */
+int dpb_fused_set_include_path(const char *colon_separated);
+/* The generated source (NUL-terminated, cut to buf_len); *needed = bytes for all of it.  No device
+ * is involved. */
+int dpb_fused_specialized_source(const dpb_fused_program *prog, char *buf, int64_t buf_len, int64_t *needed);
+/* Compiles the program without loading or launching it (no device needed: sm_100a is assumed when
+ * there is none); *cubin_bytes = size of the device code. */
+int dpb_fused_specialize_compile(const dpb_fused_program *prog, int64_t *cubin_bytes);
+
 /* ------------------------------------------------------- device-side fill */
 /* Counter-based uniform generator: element i of the output depends only on
  * (seed, i), so any shard of an array can be produced independently.

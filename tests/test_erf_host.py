@@ -1,9 +1,9 @@
 """The double-precision erf of the kernels (dpnp_b200/csrc/ew_erf.cuh) compiled for the HOST and
-measured against correctly rounded values (mpmath).  The part written in this library -- the form
-for |x| < 1/2, where the CUDA math library's erf exceeds one unit in the last place -- is the same
-source on the host and on the device; for larger arguments the host build calls the host's libm and
-the device build the CUDA math library, which tests/test_gpu_elementwise.py measures on the device.
-With an error below 1 ulp, any reference whose erf is accurate to 1 ulp is at most 2 ulp away."""
+measured against correctly rounded values (mpmath).  The function is the same source on the host and
+on the device (the series below 1/16, the table-driven Taylor step up to 6); only the table's memory
+space and the way the index is read from the rounded sum differ.  tests/test_gpu_elementwise.py repeats
+the measurement on the device.  With an error below 1 ulp, any reference whose erf is accurate to 1 ulp
+is at most 2 ulp away."""
 
 import ctypes as C
 import os
@@ -59,7 +59,7 @@ def test_erf_special_values(erf_host):
     assert got[3] == 0.0 and not np.signbit(got[3]) and got[4] == 0.0 and np.signbit(got[4])
     assert got[5] == 1.0 and got[6] == -1.0 and got[7] == 1.0
     assert got[8] == 5e-324 * 1.0 or got[8] == 1e-323      # 2/sqrt(pi) times the smallest subnormal
-    # odd function, monotone across the switch between the two forms
+    # odd function, monotone across the table intervals and the switch between the two forms
     x = np.linspace(0.0, 6.0, 48001)
     y = erf_host(x)
     assert (np.diff(y) >= 0).all() and np.array_equal(erf_host(-x), -y)

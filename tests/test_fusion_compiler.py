@@ -272,3 +272,52 @@ def test_what_is_not_fused():
     no(lambda x: x * np.float32(2), spec)                         # NumPy scalar of another type
     f = dp.fuse(lambda x: x * 2.0)
     assert f.program(spec) is not None
+
+
+def test_specialised_source_has_one_statement_per_instruction_and_compiles():
+    """The program written out as CUDA C++ for the run-time compiler: every instruction is one call
+    of the operator class the per-op kernels use, in program order; with NVRTC present the source
+    compiles for sm_100a on a machine without a GPU."""
+    import ctypes as C
+
+    from dpnp_b200 import _lib
+
+    fused = dp.fuse(lambda *a: black_scholes(dp, *a, 0.1, 0.2))
+    specs = [F.ArraySpec("f8", (4096,)) for _ in range(5)]
+    prog = fused.program(*specs)
+    assert prog is not None, fused.last_reason
+    src = prog.source()
+    body = src[src.index("__device__ __forceinline__ void chain("):src.index('extern "C" __global__')]
+    statements = [ln.strip() for ln in body.splitlines() if ln.strip().startswith(("acc =", "y"))]
+    listing = prog.listing()
+    assert len(statements) == len(listing)
+    classes = {"divide": "TrueDivideOp", "log": "LogOp", "multiply": "MultiplyOp", "sqrt": "SqrtOp",
+               "subtract": "SubtractOp", "add": "AddOp", "erf": "ErfOp", "exp": "ExpOp"}
+    for stmt, (name, dst, a, b, c3) in zip(statements, listing):
+        if name == "store":
+            assert stmt.startswith(f"y{b} =")
+        else:
+            assert classes[name] + "<T" in stmt, (stmt, name)
+    assert src.count("ErfOp<T>::apply") == 2 and "typedef double T;" in src
+    assert "const T x2" in src and "T &y1" in src                     # 3 inputs, 2 outputs
+    f4 = dp.fuse(lambda x, s: dp.where(x > s, x, 0.5) * s)
+    p4 = f4.program(F.ArraySpec("f4", (100,)), F.ArraySpec("f4", (1,)))
+    assert p4 is not None, f4.last_reason
+    s4 = p4.source()
+    assert "typedef float T;" in s4 and "const T s1 = a.in[1][0];" in s4 and "GreaterOp<T, T>" in s4
+    # NVRTC present (it ships with the CUDA toolkit): the source compiles without a device
+    try:
+        C.CDLL("libnvrtc.so.12")
+    except OSError:
+        pytest.skip("NVRTC is not installed here")
+    assert prog.compile() > 10000 and p4.compile() > 1000
+    # headers that cannot be found: the compiler's message comes back
+    _lib.check(_lib.lib.dpb_fused_set_include_path(b"/nonexistent"))
+    try:
+        other = dp.fuse(lambda x: dp.cos(x) - 3.0).program(F.ArraySpec("f8", (10,)))
+        with pytest.raises(RuntimeError, match="ew_ops.cuh"):
+            other.compile()
+    finally:
+        _lib.check(_lib.lib.dpb_fused_set_include_path(None))
+    with pytest.raises(ValueError):
+        dp.fuse(lambda x: x, mode="fast")

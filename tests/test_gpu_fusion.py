@@ -1,5 +1,7 @@
 """``dpnp_b200.fuse`` on the device: a fused chain must give the bits of the same chain run
-op by op (which the other GPU tests pin against the CPU oracle), in one launch."""
+op by op (which the other GPU tests pin against the CPU oracle), in one launch.  Every test runs
+with both executors of a fused program: the kernel compiled for the chain at run time and the
+interpreter."""
 
 import ctypes as C
 
@@ -9,6 +11,14 @@ import pytest
 from oracle import dpnp_oracle as orc
 
 pytestmark = pytest.mark.gpu
+
+KERNEL = {"compile": "ew_fused_specialized", "interpret": "ew_fused"}
+
+
+@pytest.fixture(autouse=True, params=["compile", "interpret"])
+def fuse_mode(request, monkeypatch):
+    monkeypatch.setenv("DPNP_B200_FUSE", request.param)
+    return request.param
 
 
 def black_scholes(xp, price, strike, t, rate, vol, call, put):
@@ -31,7 +41,7 @@ def black_scholes(xp, price, strike, t, rate, vol, call, put):
 
 
 @pytest.mark.parametrize("n", [1, 5, 1023, 1024, 1025, 4099, 1 << 20])
-def test_black_scholes_fused_equals_op_by_op(n):
+def test_black_scholes_fused_equals_op_by_op(n, fuse_mode):
     import dpnp_b200 as dp
     from dpnp_b200 import _lib
 
@@ -45,7 +55,8 @@ def test_black_scholes_fused_equals_op_by_op(n):
     _lib.reset_launch_count()
     fused(dP, dS, dT, 0.1, 0.2, call1, put1)
     assert fused.fused_calls == 1, fused.last_reason
-    assert _lib.launch_count() == 1 and _lib.last_kernel() == "ew_fused"
+    assert _lib.launch_count() == 1 and _lib.last_kernel() == KERNEL[fuse_mode]
+    assert fused.last_executor == {"compile": "specialized", "interpret": "interpreted"}[fuse_mode]
     np.testing.assert_array_equal(call1.asnumpy(), call0.asnumpy())
     np.testing.assert_array_equal(put1.asnumpy(), put0.asnumpy())
     # and the chain itself is within the oracle's tolerance of the exact values
@@ -188,7 +199,7 @@ def test_calls_that_are_not_fused_run_op_by_op():
     flat = dp.asarray(np.arange(20.0))
     np.testing.assert_array_equal(k(flat[:10], flat[5:15]).asnumpy(), np.arange(10.0) + np.arange(5.0, 15.0))
     assert "overlapping" in k.last_reason
-    assert _lib.last_kernel() != "ew_fused"
+    assert _lib.last_kernel() not in KERNEL.values()
 
 
 def test_c_abi_rejects_malformed_programs():
@@ -286,3 +297,32 @@ def test_random_chains_fused_equal_op_by_op(seed):
         np.testing.assert_array_equal(g.asnumpy().view(ut), r.asnumpy().view(ut))
     for u, v in zip(a0, a1):
         np.testing.assert_array_equal(u.asnumpy().view(ut), v.asnumpy().view(ut))
+
+
+def test_auto_mode_compiles_where_the_compiler_is_found_and_explicit_modes_are_checked(monkeypatch):
+    import dpnp_b200 as dp
+    from dpnp_b200 import _fusion, _lib
+
+    monkeypatch.setenv("DPNP_B200_FUSE", "auto")
+    x = dp.asarray(np.linspace(-2, 2, 1001))
+    f = dp.fuse(lambda v: dp.exp(v) * 2.0 - v)
+    want = (dp.exp(x) * 2.0 - x).asnumpy()
+    np.testing.assert_array_equal(f(x).asnumpy(), want)
+    assert f.last_executor == ("specialized" if _fusion.specialize_available() else "interpreted")
+    # the decorator's own mode wins over the environment
+    g = dp.fuse(lambda v: dp.exp(v) * 2.0 - v, mode="interpret")
+    np.testing.assert_array_equal(g(x).asnumpy(), want)
+    assert g.last_executor == "interpreted" and _lib.last_kernel() == "ew_fused"
+    with pytest.raises(ValueError):
+        dp.fuse(lambda v: v, mode="fast")
+    # headers that cannot be found: "compile" reports the compiler's message, "auto" interprets
+    _lib.check(_lib.lib.dpb_fused_set_include_path(b"/nonexistent"))
+    try:
+        h = dp.fuse(lambda v: dp.sin(v) + 1.0, mode="compile")
+        with pytest.raises(RuntimeError, match="ew_ops.cuh"):
+            h(x)
+        k = dp.fuse(lambda v: dp.sin(v) + 1.0, mode="auto")
+        np.testing.assert_array_equal(k(x).asnumpy(), (dp.sin(x) + 1.0).asnumpy())
+        assert k.last_executor == "interpreted"
+    finally:
+        _lib.check(_lib.lib.dpb_fused_set_include_path(None))
