@@ -101,6 +101,8 @@ const DeviceProps &device_props()
 
 static std::atomic<int64_t> g_ctas_per_sm{8};
 int64_t tuning_ctas_per_sm() { return g_ctas_per_sm.load(std::memory_order_relaxed); }
+static std::atomic<int64_t> g_scan_polls{-1};
+int64_t tuning_scan_lookback_polls() { return g_scan_polls.load(std::memory_order_relaxed); }
 static std::atomic<int64_t> g_fused_elems{8};
 int64_t tuning_fused_elems() { return g_fused_elems.load(std::memory_order_relaxed); }
 
@@ -215,6 +217,10 @@ int dpb_set_tuning(const char *key, int64_t value)
     }
     if (key && std::strcmp(key, "fused_elems_per_thread") == 0 && (value == 4 || value == 8)) {
         g_fused_elems.store(value);
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "scan_lookback_polls") == 0 && value >= -1 && value <= (int64_t(1) << 30)) {
+        g_scan_polls.store(value);
         return DPB_OK;
     }
     if (key && std::strcmp(key, "redzones") == 0 && (value == 0 || value == 1)) {

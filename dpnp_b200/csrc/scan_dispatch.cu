@@ -11,6 +11,9 @@
 
 namespace dpb {
 
+// probes per wait of the single-pass scan; -1: long rows take the three-launch path instead
+int64_t tuning_scan_lookback_polls();
+
 struct ScanPlan {
     RedMeta iter;        // leading (not scanned) dimensions, collapsed; strides of src and dst
     int iter_nd = 0;
@@ -94,6 +97,70 @@ template <class R> int launch_scan(const ScanPlan &plan, const void *vsrc, void 
         nseg = std::max<int64_t>(1, std::min<int64_t>(nseg, 4096));
         seg_len = ceil_div(ceil_div(L, nseg), chunk) * chunk;
         nseg = ceil_div(L, seg_len);
+    }
+    // A few long unit-stride rows: one pass over the data, tiles chained through published totals
+    // (scan_lookback_kernel).  The two repair launches return at once unless a wait ran out.
+    const int64_t polls = tuning_scan_lookback_polls();
+    const int64_t ntiles = ceil_div(L, chunk);
+    if (nseg > 1 && unit && polls >= 0 && nrows * ntiles < (int64_t(1) << 30)) {
+        LookbackLayout lay;
+        lay.levels = 0;
+        lay.per_row = 0;
+        for (int64_t cnt = ntiles; lay.levels < kLookbackLevels; cnt = ceil_div(cnt, 32)) {
+            lay.n[lay.levels] = cnt;
+            lay.off[lay.levels] = lay.per_row;
+            lay.per_row += cnt;
+            ++lay.levels;
+            if (cnt <= 32) break;
+        }
+        for (int i = lay.levels; i < kLookbackLevels; ++i) lay.n[i] = lay.off[i] = 0;
+        if (lay.n[lay.levels - 1] <= 32) {
+            const int64_t entries = nrows * lay.per_row, tiles = nrows * ntiles;
+            // values | flags | done words | error
+            using Entries = LookbackEntries<Acc>;
+            const size_t val_bytes = (static_cast<size_t>(entries) * Entries::kValueBytes + 15) / 16 * 16;
+            const size_t word_bytes = static_cast<size_t>(entries + tiles + 1) * sizeof(unsigned);
+            void *scratch = nullptr;
+            DPB_TRY(dpb_malloc(val_bytes + word_bytes, stream, &scratch));
+            Entries ent;
+            ent.vals = scratch;
+            ent.flags = reinterpret_cast<unsigned *>(static_cast<char *>(scratch) + val_bytes);
+            unsigned *done = ent.flags + entries, *error = done + tiles;
+            int st = DPB_OK;
+            if (cudaMemsetAsync(scratch, 0, val_bytes + word_bytes, stream) != cudaSuccess) {
+                cudaGetLastError();
+                st = set_error(DPB_ERR_CUDA, "scan: clearing the entries failed");
+            }
+            note_copy("memset");
+            const int max_polls = static_cast<int>(std::min<int64_t>(polls, int64_t(1) << 30));
+#define DPB_LOOKBACK_LAUNCH(VEC)                                                                      \
+    scan_lookback_kernel<R, ITEMS, VEC><<<static_cast<int>(tiles), kScanThreads, 0, stream>>>(          \
+        src, dst, plan.iter, L, ntiles, lay, ent, done, error, max_polls, plan.dst_shift)
+#define DPB_LOOKBACK_REPAIR(VEC)                                                                      \
+    scan_lookback_repair_kernel<R, ITEMS, VEC><<<red_grid(tiles), kScanThreads, 0, stream>>>(           \
+        src, dst, plan.iter, nrows, L, ntiles, lay, ent, done, error, plan.dst_shift)
+            if (st == DPB_OK) {
+                if (vec) DPB_LOOKBACK_LAUNCH(true);
+                else DPB_LOOKBACK_LAUNCH(false);
+                st = check_launch("scan_lookback");
+            }
+            if (st == DPB_OK) {
+                scan_lookback_levels_kernel<R><<<1, 1024, 0, stream>>>(ent, lay, nrows, error);
+                note_kernel("scan_lookback_levels");
+                st = check_launch("scan_lookback_levels");
+            }
+            if (st == DPB_OK) {
+                if (vec) DPB_LOOKBACK_REPAIR(true);
+                else DPB_LOOKBACK_REPAIR(false);
+                note_kernel("scan_lookback_repair");
+                st = check_launch("scan_lookback_repair");
+            }
+            note_kernel(vec ? "scan_lookback_vec" : "scan_lookback");   // the pass that does the work, named last
+#undef DPB_LOOKBACK_REPAIR
+#undef DPB_LOOKBACK_LAUNCH
+            dpb_free(scratch, stream);
+            return st;
+        }
     }
     const int grid = red_grid(nrows * nseg);
 #define DPB_SCAN_LAUNCH(UNIT, VEC, TOT, CARRY, TOTALS)                                                  \

@@ -680,6 +680,11 @@ void dpb_reset_launch_count(void);
 /* Run-time switches; DPB_ERR_VALUE for unknown keys or values out of range.
  *   "ctas_per_sm" (1..64)              resident blocks per SM assumed when sizing grids
  *   "fused_elems_per_thread" (4 | 8)   elements per thread of the fused-chain interpreter
+ *   "scan_lookback_polls" (-1 .. 2^30) probes per wait of the single-pass scan of long rows before a
+ *                                      tile gives up and is redone by the repair launches (0 makes
+ *                                      every wait that is not satisfied at once give up -- a test of
+ *                                      the repair path); -1 (default): long rows take the
+ *                                      three-launch scan instead
  *   "verbose" (0 | 1)                  log every kernel choice on stderr; initial value from the
  *                                      environment variable DPNP_B200_VERBOSE
  *   "redzones" (0 | 1)                 guarded pool blocks, see dpb_debug_redzone_report; initial value

@@ -223,3 +223,62 @@ def test_complex_running_sums_and_products():
             assert np.all(np.abs(got.asnumpy() - ref) <= tol * mag + 1e-30)
         u = np.exp(1j * rng.uniform(0, 6.28, 200)).astype(dt)          # unit modulus: products stay bounded
         np.testing.assert_allclose(dp.cumprod(dev(u)).asnumpy(), np.cumprod(u.astype("c16")), rtol=tol * 300, atol=tol * 300)
+
+
+LONG_ROWS = [((1 << 22,), "f4"), ((3, 1 << 20), "f4"), ((1, 5_000_001), "f4"), ((2, 33 * 4096 + 7), "f4"),
+             ((1 << 21,), "f8"), ((2, 700_001), "i4"), ((1 << 20,), "c8"), ((67_108_869,), "f8")]
+
+
+@pytest.mark.parametrize("shape,dt", LONG_ROWS, ids=str)
+def test_long_rows_single_pass_its_repair_path_and_the_three_launch_scan(shape, dt):
+    """A few long rows are scanned in one pass (tiles chained through published totals).  With
+    `scan_lookback_polls` = 0 every wait that is not satisfied at once gives up, so the repair launches
+    redo those tiles: the result must have the same bits.  The three-launch scan (-1) partitions the
+    sums differently: equal for integers, within the tolerance of the sums for floats."""
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    def tune(v):
+        _lib.check(_lib.lib.dpb_set_tuning(b"scan_lookback_polls", v))
+
+    rng = np.random.default_rng(len(shape) + shape[-1])
+    if dt == "c8":
+        x = (rng.normal(0, 1, shape) + 1j * rng.normal(0, 1, shape)).astype(dt)
+    elif dt == "i4":
+        x = rng.integers(-1000, 1000, shape).astype(dt)
+    else:
+        x = rng.normal(0, 1, shape).astype(dt)
+    d = dev(x)
+    try:
+        tune(1 << 20)
+        one = dp.cumsum(d, axis=-1)
+        assert _lib.last_kernel().startswith("scan_lookback"), _lib.last_kernel()
+        one = one.asnumpy()
+        tune(0)
+        repaired = dp.cumsum(d, axis=-1).asnumpy()
+        np.testing.assert_array_equal(repaired, one)
+        inplace = dp.asarray(x)
+        dp.cumsum(inplace, axis=-1, out=inplace)                       # failed tiles must not have written
+        np.testing.assert_array_equal(inplace.asnumpy(), one)
+        tune(-1)
+        three = dp.cumsum(d, axis=-1)
+        assert _lib.last_kernel().startswith("scan_rows"), _lib.last_kernel()
+        three = three.asnumpy()
+    finally:
+        tune(-1)
+    if dt == "i4":
+        ref = np.cumsum(x, axis=-1, dtype="i8")
+        np.testing.assert_array_equal(one, ref)
+        np.testing.assert_array_equal(three, ref)
+    else:
+        wide = {"f4": "f8", "f8": np.longdouble, "c8": "c16"}[dt]
+        exact = np.cumsum(x.astype(wide), axis=-1)
+        mag = np.cumsum(np.abs(x).astype("f8"), axis=-1)
+        tol = 1e-12 if dt == "f8" else 1e-5
+        assert (np.abs(one - exact) <= tol * mag + 1e-30).all()
+        assert (np.abs(three - exact) <= tol * mag + 1e-30).all()
+    if len(shape) == 2 and shape[-1] < 3_000_000:
+        # the leading identity of include_initial shifts every store by one element (no vector stores)
+        got = dp.cumulative_sum(d, axis=-1, include_initial=True).asnumpy()
+        np.testing.assert_array_equal(got[..., 1:], one)
+        assert (got[..., 0] == 0).all()
