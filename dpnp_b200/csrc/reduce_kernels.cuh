@@ -296,29 +296,84 @@ __global__ void __launch_bounds__(kRedThreads)
             const bool simple = (red.nd == 1);
             const int64_t rs = red.strides[0][0];
             int64_t r = r_begin + ty;
-            for (; r + int64_t(UNROLL - 1) * ROWS < r_end; r += int64_t(UNROLL) * ROWS) {
-                vec_t<In, VEC> x[UNROLL];
+            if constexpr (R::kVectorStep) {
+                // first stage of argmax/argmin: the best value and its row, counted from the slab's
+                // first row in 32 bits (the launcher refuses longer slabs), stay in registers; the
+                // rows come in increasing order, so only a strictly better value replaces the best
+                using V = typename R::Val;
+                V best[VEC];
+                int brow[VEC];                       // -1: nothing seen yet
 #pragma unroll
-                for (int u = 0; u < UNROLL; ++u) {
-                    const int64_t rr = r + int64_t(u) * ROWS;
+                for (int k = 0; k < VEC; ++k) {
+                    best[k] = V{};
+                    brow[k] = -1;
+                }
+                int rel = ty;
+                for (; r + int64_t(UNROLL - 1) * ROWS < r_end; r += int64_t(UNROLL) * ROWS, rel += UNROLL * ROWS) {
+                    vec_t<In, VEC> x[UNROLL];
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const int64_t rr = r + int64_t(u) * ROWS;
+                        int64_t off, unused;
+                        if (simple) off = rr * rs;
+                        else red_offsets(red, rr, off, unused);
+                        x[u] = load_vec<vec_t<In, VEC>>(base + off);
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) {
+                            const V xv = R::value(x[u].v[k]);
+                            const bool wins = (brow[k] < 0) | R::beats(xv, best[k]);
+                            best[k] = wins ? xv : best[k];
+                            brow[k] = wins ? rel + u * ROWS : brow[k];
+                        }
+                }
+                for (; r < r_end; r += ROWS, rel += ROWS) {
                     int64_t off, unused;
-                    if (simple) off = rr * rs;
-                    else red_offsets(red, rr, off, unused);
-                    x[u] = load_vec<vec_t<In, VEC>>(base + off);
+                    if (simple) off = r * rs;
+                    else red_offsets(red, r, off, unused);
+                    vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(base + off);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) {
+                        const V xv = R::value(x.v[k]);
+                        const bool wins = (brow[k] < 0) | R::beats(xv, best[k]);
+                        best[k] = wins ? xv : best[k];
+                        brow[k] = wins ? rel : brow[k];
+                    }
                 }
 #pragma unroll
-                for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-                    for (int k = 0; k < VEC; ++k)
-                        lanes[k] = R::step(lanes[k], x[u].v[k], r + int64_t(u) * ROWS);
+                for (int k = 0; k < VEC; ++k)
+                    if (brow[k] >= 0) {
+                        lanes[k].val = best[k];
+                        lanes[k].idx = r_begin + brow[k];
+                    }
             }
-            for (; r < r_end; r += ROWS) {
-                int64_t off, unused;
-                if (simple) off = r * rs;
-                else red_offsets(red, r, off, unused);
-                vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(base + off);
+            else {
+                for (; r + int64_t(UNROLL - 1) * ROWS < r_end; r += int64_t(UNROLL) * ROWS) {
+                    vec_t<In, VEC> x[UNROLL];
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) lanes[k] = R::step(lanes[k], x.v[k], r);
+                    for (int u = 0; u < UNROLL; ++u) {
+                        const int64_t rr = r + int64_t(u) * ROWS;
+                        int64_t off, unused;
+                        if (simple) off = rr * rs;
+                        else red_offsets(red, rr, off, unused);
+                        x[u] = load_vec<vec_t<In, VEC>>(base + off);
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k)
+                            lanes[k] = R::step(lanes[k], x[u].v[k], r + int64_t(u) * ROWS);
+                }
+                for (; r < r_end; r += ROWS) {
+                    int64_t off, unused;
+                    if (simple) off = r * rs;
+                    else red_offsets(red, r, off, unused);
+                    vec_t<In, VEC> x = load_vec<vec_t<In, VEC>>(base + off);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) lanes[k] = R::step(lanes[k], x.v[k], r);
+                }
             }
         }
         if constexpr (ROWS > 1) {

@@ -173,13 +173,15 @@ int launch_outer(const typename R::In *arg, void *res, const RedMeta &batch, con
     constexpr int VEC = outer_vec<R>();
     constexpr int UNROLL = 4;
     const bool vec = vector_ok && VEC > 1;
+    // the searches count rows inside a slab in 32 bits
+    if (slab_len > 0x7fffffff) return set_error(DPB_ERR_RUNTIME, "reduction range of %lld rows is too long", static_cast<long long>(slab_len));
     if (columns_per_thread) {
         const int64_t ncg = ceil_div(C, int64_t(kRedThreads) * (vec ? VEC : 1));
         const int64_t nblocks = nbatch * nslab * ncg;
         const int grid = static_cast<int>(std::min<int64_t>(nblocks, int64_t(1) << 30));
         // loads in flight per thread: fewer for wide accumulators (value + index), which
         // otherwise cost the registers that occupancy needs
-        constexpr int UC = sizeof(typename R::Acc) > 8 ? UNROLL : 2 * UNROLL;
+        constexpr int UC = (sizeof(typename R::Acc) > 8 && !R::kVectorStep) ? UNROLL : 2 * UNROLL;
         if (vec)
             reduce_outer_kernel<R, VEC, UC, 1><<<grid, kRedThreads, 0, stream>>>(
                 arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);

@@ -160,9 +160,12 @@ template <bool IS_MAX, class TIn, class TOut, class TAcc = acc_of_t<TOut>> struc
     {
         if constexpr (is_bool_v<Acc>) return IS_MAX ? bool_t(a.v || b.v) : bool_t(a.v && b.v);
         else if constexpr (std::is_floating_point_v<Acc> || is_cplx_v<Acc>) {
-            if (sv_nan(a)) return a;
-            if (sv_nan(b)) return b;
-            return sv_better<IS_MAX>(a, b) ? a : b;
+            // selects, not early returns: the branches cost more than the compares they skip
+            // (the first NaN wins; without NaNs the later operand wins a tie, as before)
+            Acc r = sv_better<IS_MAX>(a, b) ? a : b;
+            r = sv_nan(b) ? b : r;
+            r = sv_nan(a) ? a : r;
+            return r;
         }
         else return IS_MAX ? (a > b ? a : b) : (a < b ? a : b);
     }
@@ -222,6 +225,24 @@ struct SearchRed {
             a.idx = i;
             return a;
         }
+    }
+    // The pieces of `step` for kernels that keep the value and a short row number in registers and
+    // build the accumulator at the end: the value of an element, and whether it replaces the best
+    // one seen so far (strictly better; the first NaN beats every number and every later NaN).
+    using Val = V;
+    static DPB_D V value(const In &v)
+    {
+        if constexpr (STAGE2) return v.val;
+        else if constexpr (is_bool_v<TIn>) return v.v ? 1 : 0;
+        else return convert<V>(v);
+    }
+    static DPB_D bool beats(const V &x, const V &best)
+    {
+        if constexpr (std::is_floating_point_v<V> || is_cplx_v<V>) {
+            const bool bn = sv_nan(best), xn = sv_nan(x), better = sv_better<IS_MAX>(x, best);
+            return !bn & (xn | better);       // no short circuit: every test is a compare, not a branch
+        }
+        else return sv_better<IS_MAX>(x, best);
     }
     // Accumulate one element whose index is larger than every index this
     // accumulator has seen: it wins only if strictly better (or if nothing
