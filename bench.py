@@ -655,9 +655,10 @@ def other_configs(dp, _lib, ev, q, peak, rank, world, comm, sharded, price, stri
             q.wait()
             if comm is not None:
                 comm.host.barrier()
-            # one rank: 4 back-to-back calls per sample keep the device busy while the host
-            # is inside the next call; several ranks: one call, which may end in an exchange
-            batch = 4 if comm is None else 1
+            # 4 back-to-back calls per sample keep the device busy while the host is inside the
+            # next call -- at every N, so that the lines of different N compare like with like
+            # (with several ranks every call that ends in an exchange waits for the slowest rank)
+            batch = 4
             e0, e1 = ev.new(), ev.new()
             ev.record(e0)
             for _ in range(batch):

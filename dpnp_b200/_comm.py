@@ -236,6 +236,35 @@ class Communicator:
         h = C.c_void_p()
         check(lib.dpb_comm_init(self.rank, self.world, ident, C.byref(h)))
         self._handle = h
+        self.peer_exchange = False
+        if self.world > 1 and os.environ.get("DPNP_B200_PEER", "1") != "0":
+            self._init_peer_mailboxes()
+
+    def _init_peer_mailboxes(self):
+        """One-kernel combines over peer memory where every GPU of the group can map the others'
+        (same box, NVLink); otherwise the group keeps NCCL.  Every rank takes part in both host
+        exchanges whatever happens locally, and the switch is thrown only if all ranks succeeded."""
+        handle, where, ok = (C.c_char * 64)(), C.create_string_buffer(32), True
+        try:
+            check(lib.dpb_device_pci_bus_id(self.queue.device, where, 32))
+            check(lib.dpb_comm_peer_export(self._handle, handle, 64, None))
+        except (RuntimeError, ValueError, MemoryError):
+            ok = False
+        # one GPU per rank: kernels that wait for each other must never share a GPU
+        places = self.host.allgather_object((socket.gethostname(), where.value))
+        if len(set(places)) != self.world or len({h for h, _ in places}) != 1:
+            ok = False
+        handles = self.host.allgather(bytes(handle.raw) if ok else b"")
+        if ok and all(len(x) == 64 for x in handles):
+            try:
+                check(lib.dpb_comm_peer_attach(self._handle, b"".join(handles), self.world))
+            except (RuntimeError, ValueError):
+                ok = False
+        else:
+            ok = False
+        if all(self.host.allgather_object(ok)):
+            check(lib.dpb_comm_peer_enable(self._handle, 1))
+            self.peer_exchange = True
 
     def close(self):
         h, self._handle = self._handle, None

@@ -175,6 +175,11 @@ PROTOTYPES = {
     "dpb_comm_nccl_version": (_i, [C.POINTER(_i)]),
     "dpb_comm_unique_id": (_i, [_vp]),
     "dpb_comm_init": (_i, [_i, _i, _vp, _pvp]),
+    "dpb_device_pci_bus_id": (_i, [_i, C.c_char_p, _i]),
+    "dpb_comm_peer_export": (_i, [_vp, _vp, _i64, _pi64]),
+    "dpb_comm_peer_attach": (_i, [_vp, _vp, _i]),
+    "dpb_comm_peer_enable": (_i, [_vp, _i]),
+    "dpb_comm_peer_probe_wait": (_i, [_vp, _i64, C.POINTER(_i), _vp]),
     "dpb_comm_destroy": (_i, [_vp]),
     "dpb_comm_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
     "dpb_comm_allgather": (_i, [_vp, _vp, _vp, _i64, _vp]),

@@ -20,6 +20,7 @@
 // GPU: the only cross-GPU synchronisation is NCCL's.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
@@ -27,6 +28,9 @@
 #include "reduce_ops.cuh"
 
 namespace dpb {
+
+int64_t tuning_peer_polls();   // probes per wait of the peer exchange ("peer_polls" switch)
+
 namespace {
 
 // ---- the handful of NCCL entry points used, declared here (public API of libnccl.so.2)
@@ -89,6 +93,9 @@ int load_nccl(const char *path)
             return set_error(DPB_ERR_RUNTIME, "%s failed: %s", #expr, g_nccl.get_error_string(rc__)); \
     } while (0)
 
+constexpr int kMaxPeers = 16;                 // ranks whose mailboxes one process maps
+constexpr size_t kPeerSlotBytes = size_t(256) << 10;   // payload per rank that travels through the mailboxes
+constexpr size_t kPeerFlagStride = 32;        // one flag per 32-byte sector
 constexpr uint32_t kCommMagic = 0x44504243u;  // "DPBC"
 constexpr int kPairBytes = 32;                // one (value, index) record: 16 value bytes, index, padding
 
@@ -101,6 +108,14 @@ struct Comm {
     void *gather = nullptr;   // world x capacity bytes
     size_t capacity = 0;      // bytes per rank
     void *pair = nullptr;     // this rank's packed (value, index) record
+    // peer mailboxes (see the "peer exchange" section below)
+    bool peer_on = false;
+    void *box = nullptr;                  // this rank's mailbox (cudaMalloc: exported through IPC)
+    void *peer_box[kMaxPeers] = {};       // every rank's mailbox as mapped into this process
+    unsigned *peer_counter = nullptr;     // block counter of the exchange kernel
+    unsigned *peer_error_host = nullptr;  // pinned, mapped: set by a kernel whose wait ran out
+    unsigned *peer_error_dev = nullptr;   // the same word seen from the device
+    unsigned epoch = 0;                   // exchanges done so far
 };
 
 Comm *as_comm(void *c)
@@ -230,6 +245,221 @@ template <bool IS_MAX, class T> __global__ void pick_pair_kernel(const PairRecor
     if (out_index) *out_index = best_idx;
 }
 
+// ---------------------------------------------------------------- peer exchange
+// The payloads of the combines are small (a row of partial sums, one (value, index) record), so
+// their cost is latency.  Where every rank's GPU can map the others' memory (one box, NVLink), the
+// exchange and the fold are ONE kernel per rank and no library call:
+//   1. every block copies its share of this rank's payload into slot [set][rank] of EVERY rank's
+//      mailbox (plain stores to peer memory), fences, and counts itself done; the last block to
+//      finish writes the call's number into flag [set][rank] of every mailbox (release, system
+//      scope);
+//   2. every block waits until the flags of all ranks in its OWN mailbox carry the call's number
+//      -- a bounded wait: `max_polls` probes, after which the kernel raises the communicator's
+//      error word (in pinned host memory, so the host sees it without a copy) and returns;
+//   3. every block folds its share of the slots in rank order (loads past L1) into the result.
+// Two slot sets alternate with the call number: a rank can only be one call ahead of the slowest
+// (it needs everyone's flag of call k+1 before it can start call k+2), so the set it overwrites
+// is no longer being read.  The grid never exceeds one block per SM, so every block is resident
+// and none waits for a block that has not started.  A mailbox is 2 sets x world slots of 256 KiB
+// plus the flags; larger payloads go through NCCL.
+struct PeerArgs {
+    void *box[kMaxPeers];
+    int rank, world, set;
+    unsigned epoch;
+    unsigned *counter;
+    unsigned *error;
+    int max_polls;
+};
+
+DPB_D char *peer_slot(const PeerArgs &a, int owner, int src)
+{
+    return static_cast<char *>(a.box[owner]) + (size_t(a.set) * a.world + src) * kPeerSlotBytes;
+}
+DPB_D unsigned *peer_flag(const PeerArgs &a, int owner, int src)
+{
+    return reinterpret_cast<unsigned *>(static_cast<char *>(a.box[owner]) + 2 * size_t(a.world) * kPeerSlotBytes +
+                                        (size_t(a.set) * a.world + src) * kPeerFlagStride);
+}
+inline size_t peer_box_bytes(int world) { return 2 * size_t(world) * (kPeerSlotBytes + kPeerFlagStride); }
+
+// Steps 1 and 2 for `nbytes` at `send`; called by all threads of all blocks.  false: the wait ran out.
+DPB_D bool peer_exchange(const PeerArgs &a, const void *send, size_t nbytes)
+{
+    __shared__ int s_last, s_fail;
+    const size_t gtid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, gsize = size_t(gridDim.x) * blockDim.x;
+    if (((reinterpret_cast<uintptr_t>(send) | nbytes) & 15) == 0) {
+        const uint4 *src = static_cast<const uint4 *>(send);
+        for (size_t i = gtid; i < nbytes / 16; i += gsize) {
+            const uint4 v = src[i];
+            for (int r = 0; r < a.world; ++r) reinterpret_cast<uint4 *>(peer_slot(a, r, a.rank))[i] = v;
+        }
+    }
+    else {
+        const unsigned char *src = static_cast<const unsigned char *>(send);
+        for (size_t i = gtid; i < nbytes; i += gsize) {
+            const unsigned char v = src[i];
+            for (int r = 0; r < a.world; ++r) reinterpret_cast<unsigned char *>(peer_slot(a, r, a.rank))[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        if (threadIdx.x < a.world)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag(a, threadIdx.x, a.rank)), "r"(a.epoch) : "memory");
+        if (threadIdx.x == 0) *a.counter = 0;     // for the next call (this kernel is long done by then)
+    }
+    if (threadIdx.x < a.world) {
+        const unsigned *f = peer_flag(a, a.rank, threadIdx.x);
+        int polls = 0;
+        while (true) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v == a.epoch) break;
+            if (polls >= a.max_polls) {
+                s_fail = 1;
+                break;
+            }
+            ++polls;
+            if (polls > 64) __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (threadIdx.x == 0) {
+            *reinterpret_cast<volatile unsigned *>(a.error) = 1u;
+            __threadfence_system();
+        }
+        return false;
+    }
+    return true;
+}
+
+template <class T> DPB_D T peer_load(const T *p)
+{
+    // past L1: the slot was written by another GPU
+    if constexpr (sizeof(T) == 16) {
+        const uint4 w = __ldcg(reinterpret_cast<const uint4 *>(p));
+        T v;
+        memcpy(&v, &w, 16);
+        return v;
+    }
+    else if constexpr (sizeof(T) == 8) {
+        const unsigned long long w = __ldcg(reinterpret_cast<const unsigned long long *>(p));
+        T v;
+        memcpy(&v, &w, 8);
+        return v;
+    }
+    else if constexpr (sizeof(T) == 4) {
+        const unsigned w = __ldcg(reinterpret_cast<const unsigned *>(p));
+        T v;
+        memcpy(&v, &w, 4);
+        return v;
+    }
+    else if constexpr (sizeof(T) == 2) {
+        const unsigned short w = __ldcg(reinterpret_cast<const unsigned short *>(p));
+        T v;
+        memcpy(&v, &w, 2);
+        return v;
+    }
+    else {
+        const unsigned char w = __ldcg(reinterpret_cast<const unsigned char *>(p));
+        T v;
+        memcpy(&v, &w, 1);
+        return v;
+    }
+}
+
+// exchange + fold of `count` partial results per rank, in rank order
+template <class R>
+__global__ void __launch_bounds__(256)
+    peer_combine_kernel(PeerArgs a, const typename R::In *partial, typename R::Out *out, int64_t count)
+{
+    using In = typename R::In;
+    if (!peer_exchange(a, partial, size_t(count) * sizeof(In))) return;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += int64_t(gridDim.x) * blockDim.x) {
+        typename R::Acc acc = R::load(peer_load(reinterpret_cast<const In *>(peer_slot(a, a.rank, 0)) + i), 0);
+        for (int r = 1; r < a.world; ++r)
+            acc = R::combine(acc, R::load(peer_load(reinterpret_cast<const In *>(peer_slot(a, a.rank, r)) + i), 0));
+        out[i] = R::finish(acc);
+    }
+}
+
+// exchange of the ranks' (value, index) records; the records land in `recs` for pick_pair_kernel's rule
+__global__ void __launch_bounds__(256) peer_records_kernel(PeerArgs a, const PairRecord *mine, PairRecord *recs)
+{
+    if (!peer_exchange(a, mine, sizeof(PairRecord))) return;
+    if (threadIdx.x < a.world) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(peer_slot(a, a.rank, threadIdx.x));
+        uint4 *dst = reinterpret_cast<uint4 *>(recs + threadIdx.x);
+        dst[0] = __ldcg(src);
+        dst[1] = __ldcg(src + 1);
+    }
+}
+
+// a wait that nothing satisfies: the bounded wait's give-up path, for tests
+__global__ void peer_probe_wait_kernel(PeerArgs a, unsigned *timed_out)
+{
+    const unsigned *f = peer_flag(a, a.rank, 0);
+    int polls = 0;
+    unsigned result = 0;
+    while (true) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if (v == 0xffffffffu) break;              // never written: call numbers start at 1 and count up
+        if (polls >= a.max_polls) {
+            result = 1;
+            break;
+        }
+        ++polls;
+        if (polls > 64) __nanosleep(200);
+    }
+    *reinterpret_cast<volatile unsigned *>(timed_out) = result;
+    __threadfence_system();
+}
+
+// Arguments of the next exchange; DPB_ERR_RUNTIME if an earlier one gave up.
+int peer_next(Comm *c, PeerArgs &a)
+{
+    if (*reinterpret_cast<volatile unsigned *>(c->peer_error_host) != 0)
+        return set_error(DPB_ERR_RUNTIME, "a rank did not deliver its part of an earlier exchange within the time limit; "
+                                          "the communicator is unusable");
+    ++c->epoch;
+    for (int r = 0; r < kMaxPeers; ++r) a.box[r] = r < c->world ? c->peer_box[r] : nullptr;
+    a.rank = c->rank;
+    a.world = c->world;
+    a.set = static_cast<int>(c->epoch & 1u);
+    a.epoch = c->epoch;
+    a.counter = c->peer_counter;
+    a.error = c->peer_error_dev;
+    a.max_polls = static_cast<int>(tuning_peer_polls());
+    return DPB_OK;
+}
+
+inline bool peer_fits(const Comm *c, size_t nbytes) { return c->peer_on && c->world > 1 && nbytes <= kPeerSlotBytes; }
+
+inline int peer_grid(size_t nbytes)
+{
+    const int64_t want = ceil_div(static_cast<int64_t>(nbytes), 256 * 16);
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, device_props().sm_count)));
+}
+
+// exchange and fold in one kernel over the peer mailboxes
+template <class R> int launch_peer_combine(Comm *c, const void *partial, void *out, int64_t count, cudaStream_t s, const char *name)
+{
+    PeerArgs a;
+    DPB_TRY(peer_next(c, a));
+    peer_combine_kernel<R><<<peer_grid(size_t(count) * sizeof(typename R::In)), 256, 0, s>>>(
+        a, static_cast<const typename R::In *>(partial), static_cast<typename R::Out *>(out), count);
+    note_kernel(name);
+    return check_launch(name);
+}
+
 template <class R> int launch_combine(Comm *c, void *out, int64_t count, cudaStream_t s, const char *name)
 {
     const int threads = 256;
@@ -321,6 +551,12 @@ int dpb_comm_destroy(void *comm)
     cudaDeviceSynchronize();
     if (c->gather) dpb_free(c->gather, nullptr);
     if (c->pair) dpb_free(c->pair, nullptr);
+    for (int r = 0; r < c->world && r < kMaxPeers; ++r)
+        if (c->peer_box[r] && r != c->rank) cudaIpcCloseMemHandle(c->peer_box[r]);
+    if (c->box) cudaFree(c->box);
+    if (c->peer_counter) cudaFree(c->peer_counter);
+    if (c->peer_error_host) cudaFreeHost(c->peer_error_host);
+    cudaGetLastError();
     if (c->nccl) g_nccl.comm_destroy(c->nccl);
     c->magic = 0;
     delete c;
@@ -334,6 +570,98 @@ int dpb_comm_info(void *comm, int *rank, int *world)
     if (rank) *rank = c->rank;
     if (world) *world = c->world;
     return DPB_OK;
+}
+
+int dpb_comm_peer_export(void *comm, void *handle, int64_t handle_capacity, int64_t *handle_bytes)
+{
+    Comm *c = as_comm(comm);
+    if (!c) return set_error(DPB_ERR_VALUE, "not a communicator");
+    if (handle_bytes) *handle_bytes = static_cast<int64_t>(sizeof(cudaIpcMemHandle_t));
+    if (!handle || handle_capacity < static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)))
+        return set_error(DPB_ERR_VALUE, "dpb_comm_peer_export: the handle needs %d bytes", int(sizeof(cudaIpcMemHandle_t)));
+    if (c->world > kMaxPeers) return set_error(DPB_ERR_RUNTIME, "peer mailboxes serve at most %d ranks", kMaxPeers);
+    DPB_CUDA_TRY(cudaSetDevice(c->device));
+    if (!c->box) {
+        // plain cudaMalloc: memory of the stream-ordered pool cannot be exported
+        DPB_CUDA_TRY(cudaMalloc(&c->box, peer_box_bytes(c->world)));
+        DPB_CUDA_TRY(cudaMemset(c->box, 0, peer_box_bytes(c->world)));
+        DPB_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&c->peer_counter), sizeof(unsigned)));
+        DPB_CUDA_TRY(cudaMemset(c->peer_counter, 0, sizeof(unsigned)));
+        DPB_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&c->peer_error_host), sizeof(unsigned), cudaHostAllocMapped));
+        *c->peer_error_host = 0;
+        DPB_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->peer_error_dev), c->peer_error_host, 0));
+        DPB_CUDA_TRY(cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t h;
+    DPB_CUDA_TRY(cudaIpcGetMemHandle(&h, c->box));
+    std::memcpy(handle, &h, sizeof h);
+    return DPB_OK;
+}
+
+int dpb_comm_peer_attach(void *comm, const void *handles, int count)
+{
+    Comm *c = as_comm(comm);
+    if (!c) return set_error(DPB_ERR_VALUE, "not a communicator");
+    if (!c->box) return set_error(DPB_ERR_VALUE, "dpb_comm_peer_attach: call dpb_comm_peer_export first");
+    if (!handles || count != c->world) return set_error(DPB_ERR_VALUE, "dpb_comm_peer_attach: one handle per rank is needed");
+    DPB_CUDA_TRY(cudaSetDevice(c->device));
+    const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(handles);
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) {
+            c->peer_box[r] = c->box;
+            continue;
+        }
+        if (c->peer_box[r]) continue;
+        cudaIpcMemHandle_t hr;
+        std::memcpy(&hr, h + r, sizeof hr);
+        DPB_CUDA_TRY(cudaIpcOpenMemHandle(&c->peer_box[r], hr, cudaIpcMemLazyEnablePeerAccess));
+    }
+    return DPB_OK;
+}
+
+int dpb_comm_peer_enable(void *comm, int on)
+{
+    Comm *c = as_comm(comm);
+    if (!c) return set_error(DPB_ERR_VALUE, "not a communicator");
+    if (on) {
+        for (int r = 0; r < c->world; ++r)
+            if (!c->peer_box[r]) return set_error(DPB_ERR_VALUE, "dpb_comm_peer_enable: rank %d's mailbox is not attached", r);
+    }
+    c->peer_on = on != 0;
+    return DPB_OK;
+}
+
+int dpb_comm_peer_probe_wait(void *comm, int64_t polls, int *timed_out, void *stream)
+{
+    Comm *c = as_comm(comm);
+    if (!c) return set_error(DPB_ERR_VALUE, "not a communicator");
+    if (!c->box || !timed_out || polls < 0 || polls > (int64_t(1) << 24))
+        return set_error(DPB_ERR_VALUE, "dpb_comm_peer_probe_wait: bad arguments (export the mailbox first; at most 2^24 probes)");
+    PeerArgs a;
+    for (int r = 0; r < kMaxPeers; ++r) a.box[r] = nullptr;
+    a.box[c->rank] = c->box;
+    a.rank = c->rank;
+    a.world = c->world;
+    a.set = 0;
+    a.epoch = 0;
+    a.counter = c->peer_counter;
+    a.error = c->peer_error_dev;
+    a.max_polls = static_cast<int>(polls);
+    unsigned *word = nullptr, *word_dev = nullptr;
+    DPB_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&word), sizeof(unsigned), cudaHostAllocMapped));
+    *word = 2;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int st = DPB_OK;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&word_dev), word, 0) != cudaSuccess) st = DPB_ERR_CUDA;
+    if (st == DPB_OK) {
+        peer_probe_wait_kernel<<<1, 1, 0, s>>>(a, word_dev);
+        note_kernel("comm_peer_probe_wait");
+        st = check_launch("comm_peer_probe_wait");
+    }
+    if (st == DPB_OK && cudaStreamSynchronize(s) != cudaSuccess) st = set_error(DPB_ERR_CUDA, "dpb_comm_peer_probe_wait: the wait kernel failed");
+    *timed_out = static_cast<int>(*word);
+    cudaFreeHost(word);
+    return st;
 }
 
 int dpb_comm_allgather(void *comm, const void *send, void *recv, int64_t nbytes, void *stream)
@@ -360,10 +688,13 @@ int dpb_comm_sum_ordered(void *comm, int typenum, const void *partial, void *out
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t nbytes = static_cast<size_t>(count) * type_size(typenum);
     if (type_size(typenum) == 0) return set_error(DPB_ERR_TYPE, "dpb_comm_sum_ordered: unknown type %d", typenum);
-    DPB_TRY(gather_bytes(c, partial, nbytes, s));
+    const bool peer = peer_fits(c, nbytes);
+    if (!peer) DPB_TRY(gather_bytes(c, partial, nbytes, s));
     switch (typenum) {
-#define DPB_CASE(TN, T) \
-    case TN: return launch_combine<SumRed<T, T>>(c, out, count, s, "comm_sum_ordered");
+#define DPB_CASE(TN, T)                                                                               \
+    case TN:                                                                                          \
+        return peer ? launch_peer_combine<SumRed<T, T>>(c, partial, out, count, s, "comm_peer_sum_ordered") \
+                    : launch_combine<SumRed<T, T>>(c, out, count, s, "comm_sum_ordered");
         DPB_CASE(DPB_BOOL, bool_t)
         DPB_CASE(DPB_INT8, int8_t)
         DPB_CASE(DPB_UINT8, uint8_t)
@@ -391,10 +722,14 @@ int dpb_comm_extreme(void *comm, int typenum, int is_max, const void *partial, v
     if (count == 0) return DPB_OK;
     if (type_size(typenum) == 0) return set_error(DPB_ERR_TYPE, "dpb_comm_extreme: unknown type %d", typenum);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    DPB_TRY(gather_bytes(c, partial, static_cast<size_t>(count) * type_size(typenum), s));
+    const bool peer = peer_fits(c, static_cast<size_t>(count) * type_size(typenum));
+    if (!peer) DPB_TRY(gather_bytes(c, partial, static_cast<size_t>(count) * type_size(typenum), s));
     switch (typenum) {
 #define DPB_CASE(TN, T)                                                                                 \
     case TN:                                                                                            \
+        if (peer)                                                                                       \
+            return is_max ? launch_peer_combine<ExtremeRed<true, T, T>>(c, partial, out, count, s, "comm_peer_extreme")  \
+                          : launch_peer_combine<ExtremeRed<false, T, T>>(c, partial, out, count, s, "comm_peer_extreme"); \
         return is_max ? launch_combine<ExtremeRed<true, T, T>>(c, out, count, s, "comm_extreme")        \
                       : launch_combine<ExtremeRed<false, T, T>>(c, out, count, s, "comm_extreme");
         DPB_CASE(DPB_BOOL, bool_t)
@@ -452,7 +787,15 @@ int dpb_comm_arg_extreme(void *comm, int typenum, int is_max, const void *src, i
 #undef DPB_CASE
     note_kernel("comm_pack_pair");
     DPB_TRY(check_launch("comm_pack_pair"));
-    DPB_TRY(gather_bytes(c, mine, kPairBytes, s));
+    if (peer_fits(c, kPairBytes)) {
+        DPB_TRY(reserve(c, kPairBytes, s));
+        PeerArgs a;
+        DPB_TRY(peer_next(c, a));
+        peer_records_kernel<<<1, 256, 0, s>>>(a, mine, static_cast<PairRecord *>(c->gather));
+        note_kernel("comm_peer_records");
+        DPB_TRY(check_launch("comm_peer_records"));
+    }
+    else DPB_TRY(gather_bytes(c, mine, kPairBytes, s));
     const PairRecord *recs = static_cast<const PairRecord *>(c->gather);
     int64_t *oi = static_cast<int64_t *>(out_index);
 #define DPB_CASE(TN, T)                                                                                          \

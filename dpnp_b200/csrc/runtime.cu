@@ -101,6 +101,8 @@ const DeviceProps &device_props()
 
 static std::atomic<int64_t> g_ctas_per_sm{8};
 int64_t tuning_ctas_per_sm() { return g_ctas_per_sm.load(std::memory_order_relaxed); }
+static std::atomic<int64_t> g_peer_polls{int64_t(1) << 24};
+int64_t tuning_peer_polls() { return g_peer_polls.load(std::memory_order_relaxed); }
 static std::atomic<int64_t> g_scan_polls{-1};
 int64_t tuning_scan_lookback_polls() { return g_scan_polls.load(std::memory_order_relaxed); }
 static std::atomic<int64_t> g_fused_elems{8};
@@ -219,6 +221,10 @@ int dpb_set_tuning(const char *key, int64_t value)
         g_fused_elems.store(value);
         return DPB_OK;
     }
+    if (key && std::strcmp(key, "peer_polls") == 0 && value >= 0 && value <= (int64_t(1) << 24)) {
+        g_peer_polls.store(value);
+        return DPB_OK;
+    }
     if (key && std::strcmp(key, "scan_lookback_polls") == 0 && value >= -1 && value <= (int64_t(1) << 30)) {
         g_scan_polls.store(value);
         return DPB_OK;
@@ -247,6 +253,13 @@ int dpb_device_count(void)
         return 0;
     }
     return n;
+}
+
+int dpb_device_pci_bus_id(int device, char *buf, int len)
+{
+    if (!buf || len < 16) return set_error(DPB_ERR_VALUE, "dpb_device_pci_bus_id: a buffer of at least 16 bytes is needed");
+    DPB_CUDA_TRY(cudaDeviceGetPCIBusId(buf, len, device));
+    return DPB_OK;
 }
 
 int dpb_set_device(int device)

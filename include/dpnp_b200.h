@@ -213,6 +213,9 @@ int dpb_device_count(void);
 
 /* Make `device` current in the calling thread (cudaSetDevice). Replaces the
  * device selection implied by a SyclQueue (dpnp/tensor/_compute_follows_data.pyx:67-160). */
+/* "domain:bus:device.function" of a device (NUL-terminated, at least 16 bytes): tells two ranks
+ * whether they sit on the same GPU. */
+int dpb_device_pci_bus_id(int device, char *buf, int len);
 int dpb_set_device(int device);
 int dpb_get_device(int *device);
 
@@ -649,6 +652,25 @@ int dpb_comm_unique_id(void *id128);
 int dpb_comm_init(int rank, int world, const void *id128, void **comm);
 int dpb_comm_destroy(void *comm);
 int dpb_comm_info(void *comm, int *rank, int *world);
+/* Peer mailboxes: where every rank's GPU can map the others' memory (one box, NVLink), the combines
+ * below exchange their payloads (up to 256 KiB per rank) and fold them in ONE kernel per rank --
+ * stores into the peers' mailboxes, a flag per rank, a bounded wait, the fold in rank order --
+ * instead of an NCCL all-gather followed by a kernel.  Set-up, once per communicator:
+ *   dpb_comm_peer_export  allocates this rank's mailbox and returns its inter-process handle
+ *                         (*handle_bytes = size of a handle, 64);
+ *   (the caller makes every rank's handle known to every rank: an all-gather over its host group)
+ *   dpb_comm_peer_attach  maps the ranks' mailboxes from the `count` = world handles, in rank order;
+ *   dpb_comm_peer_enable  switches the combines over (every rank must make the same choice, so the
+ *                         caller agrees on it first: all ranks attached successfully, or none uses it).
+ * A wait that runs out ("peer_polls" probes, dpb_set_tuning) makes the kernel raise an error word in
+ * pinned host memory and return; every later combine of the communicator fails with
+ * DPB_ERR_RUNTIME.  dpb_comm_peer_probe_wait runs that bounded wait on a flag nobody sets and
+ * reports whether it gave up (*timed_out = 1): the test of the give-up path.  No counterpart in
+ * the reference. */
+int dpb_comm_peer_export(void *comm, void *handle, int64_t handle_capacity, int64_t *handle_bytes);
+int dpb_comm_peer_attach(void *comm, const void *handles, int count);
+int dpb_comm_peer_enable(void *comm, int on);
+int dpb_comm_peer_probe_wait(void *comm, int64_t polls, int *timed_out, void *stream);
 /* recv[r * nbytes ...] = rank r's send buffer (device memory, nbytes per rank). */
 int dpb_comm_allgather(void *comm, const void *send, void *recv, int64_t nbytes, void *stream);
 /* out[i] = partial_0[i] + partial_1[i] + ... in rank order, identical bits on every rank:
@@ -680,6 +702,9 @@ void dpb_reset_launch_count(void);
 /* Run-time switches; DPB_ERR_VALUE for unknown keys or values out of range.
  *   "ctas_per_sm" (1..64)              resident blocks per SM assumed when sizing grids
  *   "fused_elems_per_thread" (4 | 8)   elements per thread of the fused-chain interpreter
+ *   "peer_polls" (0 .. 2^24)           probes per wait of the peer-mailbox exchange of the combines
+ *                                      (default 2^24, the largest value: about half a minute -- the bound is
+ *                                      there for a rank that died, not for one that is late)
  *   "scan_lookback_polls" (-1 .. 2^30) probes per wait of the single-pass scan of long rows before a
  *                                      tile gives up and is redone by the repair launches (0 makes
  *                                      every wait that is not satisfied at once give up -- a test of

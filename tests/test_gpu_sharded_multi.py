@@ -1,5 +1,6 @@
-"""Sharded reductions over two GPUs with real NCCL exchanges: one child process per GPU, no
-PyTorch.  Skipped where the box shows fewer than two devices."""
+"""Sharded reductions over two GPUs with real exchanges -- through the peer mailboxes (one kernel per
+rank and combine) and through NCCL: one child process per GPU, no PyTorch.  Skipped where the box
+shows fewer than two devices."""
 
 import os
 import socket
@@ -20,8 +21,11 @@ WORKER = textwrap.dedent("""
     import dpnp_b200 as dp
     from dpnp_b200 import sharded
 
+    from dpnp_b200 import _lib
     comm = sharded.init()
     rank, world = comm.rank, comm.world
+    want_peer = os.environ.get("DPNP_B200_PEER", "1") != "0"
+    assert comm.peer_exchange == want_peer, (comm.peer_exchange, want_peer)
     rng = np.random.default_rng(0)                    # the same global arrays on every rank
     x = rng.normal(0, 1, (1001, 4099)).astype("f4")
     xs = sharded.scatter_rows(x, comm)
@@ -32,6 +36,7 @@ WORKER = textwrap.dedent("""
     exact = x.astype(np.longdouble).sum(axis=0)
     mag = np.abs(x).astype(np.longdouble).sum(axis=0)
     assert np.all(np.abs(got.astype(np.longdouble) - exact) <= 1e-5 * mag)
+    assert _lib.last_kernel() == ("comm_peer_sum_ordered" if want_peer else "comm_sum_ordered"), _lib.last_kernel()
     every = comm.host.allgather_object(got.tobytes())
     assert all(b == every[0] for b in every), "ranks disagree on the ordered sum"
     # and it is the rank-ordered float32 sum of the ranks' own partials
@@ -77,13 +82,29 @@ WORKER = textwrap.dedent("""
     np.testing.assert_array_equal(dp.argmin(st, axis=0).asnumpy(), tiny.argmin(axis=0))
     np.testing.assert_array_equal(st.asnumpy(), tiny)
     np.testing.assert_array_equal(xs.asnumpy(), x)
+    # a payload beyond a mailbox slot (256 KiB per rank) takes the NCCL route on either setting
+    wide = rng.normal(0, 1, (4, 100_000))
+    sw = sharded.scatter_rows(wide, comm)
+    gw = dp.sum(sw, axis=0)
+    assert _lib.last_kernel() == "comm_sum_ordered", _lib.last_kernel()
+    pw = comm.host.allgather_object(dp.sum(sw.local, axis=0).asnumpy())
+    np.testing.assert_array_equal(gw.asnumpy(), pw[0] + pw[1])
+    # many combines back to back: the two slot sets alternate and no call overtakes another
+    outs = [dp.sum(xs * float(k), axis=0) for k in range(1, 41)]
+    for k in (1, 17, 40):
+        mine = dp.sum(xs.local * float(k), axis=0).asnumpy()
+        ordered = None
+        for part in comm.host.allgather_object(mine):
+            ordered = part if ordered is None else ordered + part
+        np.testing.assert_array_equal(outs[k - 1].asnumpy(), ordered)
     comm.barrier()
     comm.close()
     print("rank", rank, "ok")
 """)
 
 
-def test_two_gpus(tmp_path):
+@pytest.mark.parametrize("peer", ["1", "0"], ids=["peer_mailboxes", "nccl"])
+def test_two_gpus(tmp_path, peer):
     from dpnp_b200 import _lib
 
     if _lib.device_count() < 2:
@@ -97,7 +118,7 @@ def test_two_gpus(tmp_path):
     for rank in range(2):
         # NVLS off: a rank that dies must not leave its memory bound to a multicast object
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), REPO_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+                   MASTER_PORT=str(port), REPO_ROOT=ROOT, NCCL_NVLS_ENABLE="0", DPNP_B200_PEER=peer)
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=600)[0] for p in procs]

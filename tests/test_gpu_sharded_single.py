@@ -94,3 +94,27 @@ def test_communicator_errors(comm):
     junk = (C.c_char * 64)()
     assert _lib.lib.dpb_comm_sum_ordered(junk, 10, None, None, 4, None) != 0
     assert "not a communicator" in _lib.last_error()
+
+
+def test_the_bounded_wait_of_the_peer_exchange_gives_up_and_reports_it(comm):
+    """The peer-mailbox exchange waits for the other ranks' flags with a bounded number of probes.
+    Here the wait is run on a flag that nothing sets: it must come back, say that it gave up, and
+    leave the device and the communicator usable."""
+    import dpnp_b200 as dp
+    from dpnp_b200 import _lib
+
+    lib, check = _lib.lib, _lib.check
+    handle, size = (C.c_char * 64)(), C.c_int64()
+    check(lib.dpb_comm_peer_export(comm._handle, handle, 64, C.byref(size)))
+    assert size.value == 64
+    q = dp.get_default_queue()
+    for polls in (0, 1000):
+        gave_up = C.c_int(-1)
+        check(lib.dpb_comm_peer_probe_wait(comm._handle, polls, C.byref(gave_up), C.c_void_p(q.stream)))
+        assert gave_up.value == 1 and _lib.last_kernel() == "comm_peer_probe_wait"
+    with pytest.raises(ValueError):
+        check(lib.dpb_comm_peer_export(comm._handle, handle, 8, None))              # room for the handle
+    with pytest.raises(ValueError):
+        check(lib.dpb_comm_peer_attach(comm._handle, bytes(64), 3))                  # one handle per rank
+    x = dp.asarray(np.arange(12.0))
+    np.testing.assert_array_equal(comm.sum_ordered(x).asnumpy(), np.arange(12.0))    # still in working order
