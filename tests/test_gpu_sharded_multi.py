@@ -116,7 +116,7 @@ def test_two_gpus(tmp_path, peer):
     script.write_text(WORKER)
     procs = []
     for rank in range(2):
-        # NVLS off: a rank that dies must not leave its memory bound to a multicast object
+        # NVLS off: a rank that dies must not leave its memory bound to an NVLink switch group
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), REPO_ROOT=ROOT, NCCL_NVLS_ENABLE="0", DPNP_B200_PEER=peer)
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
