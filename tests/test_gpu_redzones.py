@@ -42,8 +42,9 @@ def _sweep(dp):
             dp.add(a, b); dp.multiply(a[::-1], b); dp.equal(a, b); dp.where(a != b, a, b)
             if dt in ("f4", "f8"):
                 dp.exp(a); dp.erf(a[::2]); dp.sum(a); dp.max(a); dp.argmax(a); dp.cumsum(a); a * 2.0
-                f = dp.fuse(lambda x, y: dp.sqrt(dp.abs(x)) * y + 1.0)
-                f(a, b)
+                for mode in ("compile", "interpret"):           # both executors of a fused chain
+                    f = dp.fuse(lambda x, y: dp.sqrt(dp.abs(x)) * y + 1.0, mode=mode)
+                    f(a, b)
     for shape in ((3, 5), (17, 33), (64, 65), (5, 7, 9), (33, 1, 31), (2, 129, 3)):
         x = dp.asarray(rng.normal(0, 1, shape).astype("f4"))
         y = dp.asarray(rng.normal(0, 1, shape[-1]).astype("f4"))
@@ -55,6 +56,15 @@ def _sweep(dp):
                 dp.argmin(x, axis=ax)
                 dp.cumsum(x, axis=ax if ax is not None else None)
         dp.astype(x, "f8"); dp.astype(x[:, ::2], "i4")
+    # the single-pass scan of long rows (opt-in), ragged last tile, and its repair launches
+    from dpnp_b200 import _lib
+    for polls in (1 << 20, 0):
+        _lib.check(_lib.lib.dpb_set_tuning(b"scan_lookback_polls", polls))
+        try:
+            for shape, dt in (((70001,), "f4"), ((2, 33 * 4096 + 5), "f4"), ((40003,), "f8")):
+                dp.cumsum(dp.asarray(rng.normal(0, 1, shape).astype(dt)), axis=-1)
+        finally:
+            _lib.check(_lib.lib.dpb_set_tuning(b"scan_lookback_polls", -1))
 
 
 def test_small_shape_sweeps_leave_the_guard_bytes_intact(guarded):
