@@ -215,3 +215,62 @@ def test_group_formation_failures_are_errors_not_hangs(tmp_path, mode):
     exception within the timeout (failure made on the host; no GPU involved)."""
     procs, outs = _run_ranks(tmp_path, 2, "tcp", {"FAIL_MODE": mode}, FAILING)
     assert procs[0].returncode == 7 and "refused" in outs[0], outs
+
+
+PEER_SETUP = textwrap.dedent("""
+    import ctypes as C, os, sys, types
+    sys.path.insert(0, os.environ["REPO_ROOT"])
+    from dpnp_b200 import _comm, sharded
+
+    mode, rank = os.environ["PEER_CASE"], int(os.environ["RANK"])
+    calls = []
+
+    class FakeLib:
+        # stands where the native calls stand: records what the set-up asks for, fails where told to
+        def dpb_device_pci_bus_id(self, device, buf, n):
+            same = mode == "shared_gpu"
+            buf.value = b"0000:17:00.0" if same else ("0000:%02x:00.0" % (0x17 + rank)).encode()
+            return 0
+        def dpb_comm_peer_export(self, handle, buf, cap, size):
+            calls.append("export")
+            if mode == "export_fails" and rank == 1:
+                return 2
+            C.memmove(buf, bytes([rank + 1]) * 64, 64)
+            return 0
+        def dpb_comm_peer_attach(self, handle, blob, count):
+            calls.append(("attach", count, bytes(blob)[:1], bytes(blob)[64:65]))
+            return 2 if (mode == "attach_fails" and rank == 0) else 0
+        def dpb_comm_peer_enable(self, handle, on):
+            calls.append(("enable", on))
+            return 0
+        def dpb_last_error(self):
+            return b"stand-in failure"
+
+    _comm.lib = FakeLib()
+    comm = _comm.Communicator(sharded.HostGroup(timeout=20.0), device_side=False)
+    comm._handle, comm.queue = C.c_void_p(1), types.SimpleNamespace(device=rank)
+    comm.peer_exchange = False
+    comm._init_peer_mailboxes()
+    expect = mode == "all_good"
+    assert comm.peer_exchange == expect, (mode, rank, comm.peer_exchange, calls)
+    assert (("enable", 1) in calls) == expect, calls
+    if mode in ("all_good", "attach_fails"):
+        att = [c for c in calls if c[0] == "attach"][0]
+        assert att[1:] == (2, b"\\x01", b"\\x02"), att            # both handles, in rank order
+    if mode == "shared_gpu":
+        assert not any(c[0] == "attach" for c in calls if isinstance(c, tuple)), calls
+    comm.host.barrier()
+    print("rank", rank, "ok")
+""")
+
+
+@pytest.mark.parametrize("case", ["all_good", "export_fails", "attach_fails", "shared_gpu"])
+def test_peer_mailboxes_are_switched_on_by_all_ranks_or_by_none(tmp_path, case):
+    """The set-up of the one-kernel combines is a collective decision made on the host: every rank
+    takes part in both exchanges whatever happened locally, the switch is thrown only if every rank
+    exported and attached, and never for two ranks on one GPU (their kernels would wait for each
+    other on the same device).  The native calls are recording stand-ins; no GPU is involved."""
+    procs, outs = _run_ranks(tmp_path, 2, "tcp", {"PEER_CASE": case}, PEER_SETUP)
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {rank} failed:\n{out}"
+        assert f"rank {rank} ok" in out
