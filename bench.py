@@ -28,7 +28,10 @@ synthetic (seeded uniform draws with the example's ranges).
 
 With N > 1 (torchrun, one rank per GPU) every rank prices its own 2^26 options
 (weak scaling, no data-path collective); the reduction configurations are
-sharded on the leading axis and combined with NCCL.
+sharded on the leading axis and their partials combined in rank order -- by one
+kernel per rank over peer mailboxes where every rank owns a GPU of one box, else
+through NCCL (`combine_us`: that step alone).  Every op is timed the same way at
+every N: 4 back-to-back calls per sample, maximum over the ranks.
 """
 
 from __future__ import annotations
