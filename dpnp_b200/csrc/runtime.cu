@@ -101,6 +101,8 @@ const DeviceProps &device_props()
 
 static std::atomic<int64_t> g_ctas_per_sm{8};
 int64_t tuning_ctas_per_sm() { return g_ctas_per_sm.load(std::memory_order_relaxed); }
+static std::atomic<int> g_pdl{1};
+bool tuning_pdl() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 static std::atomic<int64_t> g_peer_polls{int64_t(1) << 24};
 int64_t tuning_peer_polls() { return g_peer_polls.load(std::memory_order_relaxed); }
 static std::atomic<int64_t> g_scan_polls{-1};
@@ -219,6 +221,10 @@ int dpb_set_tuning(const char *key, int64_t value)
     }
     if (key && std::strcmp(key, "fused_elems_per_thread") == 0 && (value == 4 || value == 8)) {
         g_fused_elems.store(value);
+        return DPB_OK;
+    }
+    if (key && std::strcmp(key, "pdl") == 0 && (value == 0 || value == 1)) {
+        g_pdl.store(static_cast<int>(value));
         return DPB_OK;
     }
     if (key && std::strcmp(key, "peer_polls") == 0 && value >= 0 && value <= (int64_t(1) << 24)) {

@@ -702,6 +702,9 @@ void dpb_reset_launch_count(void);
 /* Run-time switches; DPB_ERR_VALUE for unknown keys or values out of range.
  *   "ctas_per_sm" (1..64)              resident blocks per SM assumed when sizing grids
  *   "fused_elems_per_thread" (4 | 8)   elements per thread of the fused-chain interpreter
+ *   "pdl" (0 | 1)                      contiguous elementwise kernels are launched with programmatic
+ *                                      stream serialisation (the launch overlaps the previous kernel's
+ *                                      tail; the kernel waits for that kernel before it reads); default 1
  *   "peer_polls" (0 .. 2^24)           probes per wait of the peer-mailbox exchange of the combines
  *                                      (default 2^24, the largest value: about half a minute -- the bound is
  *                                      there for a rank that died, not for one that is late)
