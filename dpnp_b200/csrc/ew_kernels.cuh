@@ -61,30 +61,6 @@ template <class F> constexpr int ew_vec_width()
     else return vec_width<typename F::In0, typename F::In1, typename F::In2, typename F::Out>();
 }
 
-bool tuning_pdl();   // "pdl" switch: launch the contiguous kernels with programmatic stream serialisation
-
-// Launch of a kernel that begins with cudaGridDependencySynchronize(): with the attribute below the
-// launch itself overlaps the tail of the kernel before it in the stream (measured on B200: 16
-// back-to-back additions of 2^24 float32, 32.9 us -> 30.6 us each); the kernel still starts
-// reading only after that kernel has completed and its writes are visible.
-template <class... KArgs, class... Args>
-inline void launch_after_previous(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t stream,
-                                  Args... args)
-{
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(block);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    if (tuning_pdl()) {
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-    }
-    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);   // an error stays in cudaGetLastError for check_launch
-}
-
 // 16-byte accesses per thread of the contiguous kernel for one streamed input: 8 unless the
 // functor names its own (kUnroll)
 template <class F, class = void> struct ew_unroll { static constexpr int value = 8; };
@@ -178,6 +154,7 @@ __global__ void __launch_bounds__(kEwThreads, 5)
                    int64_t nrows, int tx_log2, int64_t chunks_per_row, int64_t nwork, FastDiv32 chunk_div,
                    int head)
 {
+    cudaGridDependencySynchronize();   // see launch_after_previous
     using In0 = typename F::In0;
     using In1 = typename F::In1;
     using In2 = typename F::In2;
@@ -490,6 +467,7 @@ __global__ void __launch_bounds__(kEwThreads, 6)
     ew_transpose_vec_kernel(F f, EwPtrs<F> p, StridedMeta<F::NIN + 1> batch, int64_t np, int64_t nq,
                             TransposeStrides st, TileDivs td, uint32_t nwork, int tiles_per_block)
 {
+    cudaGridDependencySynchronize();   // see launch_after_previous
     using In0 = typename F::In0;
     using In1 = typename F::In1;
     using Out = typename F::Out;
@@ -806,8 +784,8 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
         const int64_t nwork = ceil_div(nrows, TY) * chunks;
         const FastDiv32 chunk_div(static_cast<uint32_t>(chunks < (int64_t(1) << 31) ? chunks : 1));
 #define DPB_ROWS_LAUNCH(V, MASK)                                                                    \
-    ew_rows_kernel<F, V, UNROLL, MASK><<<ew_flat_grid(nwork), kEwThreads, 0, stream>>>(              \
-        f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, head)
+    launch_after_previous(ew_rows_kernel<F, V, UNROLL, MASK>, ew_flat_grid(nwork), kEwThreads, stream, \
+                          f, p, outer, L, inner_bcast, nrows, tx_log2, chunks, nwork, chunk_div, head)
         if (vec > 1) {
             if (inner_bcast == 0) DPB_ROWS_LAUNCH(VEC, 0);
             else if (inner_bcast == 1) DPB_ROWS_LAUNCH(VEC, (F::NIN == 2 ? 1 : 0));
@@ -885,8 +863,8 @@ int launch_ew(const F &f, const EwPlan &plan, const void *const *in, void *out, 
                     const unsigned sm = plan.staged_mask;
 #define DPB_TR_LAUNCH(S, V)                                                                          \
     {                                                                                                \
-        ew_transpose_vec_kernel<F, TV, S, V><<<nblocks, kEwThreads, 0, stream>>>(f, p, batch, np, nq, ts, \
-                                                                                 td, nw32, tpb);      \
+        launch_after_previous(ew_transpose_vec_kernel<F, TV, S, V>, nblocks, kEwThreads, stream, f, p, batch, \
+                              np, nq, ts, td, nw32, tpb);                                            \
         note_kernel("ew_transpose_vec");                                                             \
         return check_launch("ew_transpose_vec");                                                     \
     }

@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(kRedThreads)
     reduce_inner_kernel(const typename R::In *arg, void *res, RedMeta iter, int64_t nrows, int64_t L,
                         int64_t nsplit, int64_t chunk, bool final_pass, int64_t index_rows)
 {
+    cudaGridDependencySynchronize();   // see launch_after_previous
     using In = typename R::In;
     using Acc = typename R::Acc;
     __shared__ Acc smem[8];
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(kRedThreads)
                         int64_t nred, int64_t nbatch, int64_t nslab, int64_t slab_len,
                         int64_t ncolgroups, bool final_pass)
 {
+    cudaGridDependencySynchronize();   // see launch_after_previous
     using In = typename R::In;
     using Acc = typename R::Acc;
     // ROWS thread rows share the reduction range of a column group; ROWS == 1 gives every

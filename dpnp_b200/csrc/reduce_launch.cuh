@@ -91,20 +91,18 @@ int launch_inner(const typename R::In *arg, void *res, const RedMeta &iter, int6
     const int64_t nitems = nrows * nsplit;
     const int64_t len = nsplit > 1 ? chunk : L;
     if (len <= 16) {
-        reduce_inner_kernel<R, 1, 1, UNROLL><<<red_grid(ceil_div(nitems, kRedThreads)), kRedThreads, 0,
-                                              stream>>>(arg, res, iter, nrows, L, nsplit, chunk,
-                                                        final_pass, index_rows);
+        launch_after_previous(reduce_inner_kernel<R, 1, 1, UNROLL>, red_grid(ceil_div(nitems, kRedThreads)), kRedThreads,
+                              stream, arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
         note_kernel("reduce_inner_thread");
     }
     else if (len <= 1024) {
-        reduce_inner_kernel<R, VEC, 32, UNROLL>
-            <<<red_grid(ceil_div(nitems, kRedThreads / 32)), kRedThreads, 0, stream>>>(
-                arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
+        launch_after_previous(reduce_inner_kernel<R, VEC, 32, UNROLL>, red_grid(ceil_div(nitems, kRedThreads / 32)),
+                              kRedThreads, stream, arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
         note_kernel("reduce_inner_warp");
     }
     else {
-        reduce_inner_kernel<R, VEC, 256, UNROLL><<<red_grid(nitems), kRedThreads, 0, stream>>>(
-            arg, res, iter, nrows, L, nsplit, chunk, final_pass, index_rows);
+        launch_after_previous(reduce_inner_kernel<R, VEC, 256, UNROLL>, red_grid(nitems), kRedThreads, stream, arg, res,
+                              iter, nrows, L, nsplit, chunk, final_pass, index_rows);
         note_kernel("reduce_inner_block");
     }
     return check_launch("reduce_inner");
@@ -183,25 +181,25 @@ int launch_outer(const typename R::In *arg, void *res, const RedMeta &batch, con
         // otherwise cost the registers that occupancy needs
         constexpr int UC = (sizeof(typename R::Acc) > 8 && !R::kVectorStep) ? UNROLL : 2 * UNROLL;
         if (vec)
-            reduce_outer_kernel<R, VEC, UC, 1><<<grid, kRedThreads, 0, stream>>>(
-                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+            launch_after_previous(reduce_outer_kernel<R, VEC, UC, 1>, grid, kRedThreads, stream, arg, res, batch, red, C,
+                                  nred, nbatch, nslab, slab_len, ncg, final_pass);
         else
-            reduce_outer_kernel<R, 1, UC, 1><<<grid, kRedThreads, 0, stream>>>(
-                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+            launch_after_previous(reduce_outer_kernel<R, 1, UC, 1>, grid, kRedThreads, stream, arg, res, batch, red, C,
+                                  nred, nbatch, nslab, slab_len, ncg, final_pass);
         note_kernel(vec ? "reduce_outer_cols_vec" : "reduce_outer_cols_scalar");
     }
     else if (vec) {
         const int64_t ncg = ceil_div(C, 32 * VEC);
-        reduce_outer_kernel<R, VEC, UNROLL, kOuterRows>
-            <<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
-                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        launch_after_previous(reduce_outer_kernel<R, VEC, UNROLL, kOuterRows>, red_grid(nbatch * nslab * ncg),
+                              kRedThreads, stream, arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg,
+                              final_pass);
         note_kernel("reduce_outer_vec");
     }
     else {
         const int64_t ncg = ceil_div(C, 32);
-        reduce_outer_kernel<R, 1, UNROLL, kOuterRows>
-            <<<red_grid(nbatch * nslab * ncg), kRedThreads, 0, stream>>>(
-                arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg, final_pass);
+        launch_after_previous(reduce_outer_kernel<R, 1, UNROLL, kOuterRows>, red_grid(nbatch * nslab * ncg),
+                              kRedThreads, stream, arg, res, batch, red, C, nred, nbatch, nslab, slab_len, ncg,
+                              final_pass);
         note_kernel("reduce_outer_scalar");
     }
     return check_launch("reduce_outer");
